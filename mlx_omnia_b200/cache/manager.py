@@ -21,7 +21,8 @@ return when the request ends. Freed pages are handed out again, last freed first
 
 Beside the pages there are *state slots*: a request holds one slot number for its
 whole life, and every entry that declares a `StateSpec` has a tensor
-`[slots + 1, *shape]` indexed by it; the last row is a scratch slot that belongs to no
+`[slots + 1, *shape]` indexed by it (an entry that declares several by name has one
+each, and so has a block that declares state of its own); the last row is a scratch slot that belongs to no
 request (the padding rows of a captured step point at it). A slot is set to the mixer's
 initial state when a request's first step runs. Muse-Glimmer declares no state; the
 slots exist so a mixer with state of its own needs no change here.
@@ -140,15 +141,44 @@ class CacheManager:
                 group.pages = torch.zeros(len(group.entries), group.pool.count, *shape, dtype=dtype, device=device)
         self.slots = PagePool(max_requests)
         self.scratch_slot = max_requests  # the state row that padding rows of a captured step point at
-        self.state: dict[int, torch.Tensor] = {}
+        self.state: dict[int, torch.Tensor | dict[str, torch.Tensor]] = {}  # a mixer's: one tensor, or by name
+        self.block_state: dict[int, dict[str, torch.Tensor]] = {}  # a block's own, by name
         self.initial_state: dict[int, torch.Tensor] = {}  # entries whose state does not start as zeros
+
+        def slots_of(spec):
+            return torch.zeros(max_requests + 1, *spec.shape, dtype=spec.dtype, device=device)
+
         for entry, need in enumerate(needs):
-            if need.state is not None and allocate:
-                self.state[entry] = torch.zeros(max_requests + 1, *need.state.shape, dtype=need.state.dtype,
-                                                device=device)
+            if not allocate:
+                continue
+            if isinstance(need.state, dict):
+                self.state[entry] = {name: slots_of(spec) for name, spec in need.state.items()}
+            elif need.state is not None:
+                self.state[entry] = slots_of(need.state)
                 if need.initial_state is not None:
                     self.initial_state[entry] = need.initial_state.to(need.state.dtype).to(device)
+            if getattr(need, "block_state", None):
+                self.block_state[entry] = {name: slots_of(spec) for name, spec in need.block_state.items()}
         self.requests: dict[str, RequestCache] = {}
+
+    def reset_slots(self, slots: list[int]) -> None:
+        """Set the state of `slots` (of requests about to run their first step) to its start:
+        the mixer's `initial_state()` where it gave one, zeros everywhere else."""
+        if not slots or not (self.state or self.block_state):
+            return
+        index = None
+        for entry in sorted(set(self.state) | set(self.block_state)):
+            held = self.state.get(entry)
+            tensors = list(held.values()) if isinstance(held, dict) else ([held] if held is not None else [])
+            tensors += list(self.block_state.get(entry, {}).values())
+            for tensor in tensors:
+                if index is None:
+                    index = torch.as_tensor(slots, device=tensor.device)
+                initial = self.initial_state.get(entry) if tensor is held else None
+                if initial is None:
+                    tensor.index_fill_(0, index, 0)
+                else:
+                    tensor[index] = initial
 
     # -- sizes -----------------------------------------------------------------------
     @staticmethod

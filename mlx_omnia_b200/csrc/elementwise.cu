@@ -456,6 +456,40 @@ extern "C" int omnia_swiglu(const void* gu, void* act, int rows, int inner, int 
 }
 
 // ---------------------------------------------------------------------------------
+// act = f(z) element by element, in float32, rounded once. kind 0: relu(z)^2; 1: the tanh form of
+// GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2: SiLU.
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ z, T* __restrict__ act, long long total, int kind) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const float v = to_f32(z[idx]);
+    float y;
+    if (kind == 0) {
+      const float r = fmaxf(v, 0.f);
+      y = r * r;
+    } else if (kind == 1) {
+      y = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    } else {
+      y = v / (1.f + expf(-v));
+    }
+    act[idx] = from_f32<T>(y);
+  }
+}
+
+extern "C" int omnia_activation(const void* z, void* act, long long total, int kind, int dtype,
+                                cudaStream_t stream) {
+  if (total == 0) return 0;
+  if (kind < 0 || kind > 2) return (int)cudaErrorInvalidValue;
+  const long long most = 16LL * omnia_sm_count();
+  const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(activation_kernel<T>, blocks, 256, 0, stream, (const T*)z, (T*)act,
+                                          total, kind)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
 // logits = cap * tanh(z * multiplier / cap)  (cap <= 0: logits = z * multiplier), float32 out.
 template <typename T>
 __global__ void softcap_kernel(const T* __restrict__ z, float* __restrict__ out, long long total,

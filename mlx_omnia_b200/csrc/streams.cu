@@ -1,0 +1,196 @@
+// The residual as several streams (hyper-connections), the grouped RMS norm and the token shift:
+// the two kernels a pre-norm block with these options runs around each of its branches.
+//
+//   enter:  u = sum_s a[s] x_s;  n = grouped_rms(u) * w;  h = n + (n_prev - n) * mu     (mu optional)
+//   leave:  x_t <- sum_s M[s, t] x_s + b[t] * y    for all t at once                    (M, b optional: x += y)
+//
+// x is float32 [tokens, S, D] (S = 1: the plain residual). One block per token. All arithmetic is
+// float32; only h and y have the engine's element type. The order of every sum depends on the
+// sizes alone, never on how a batch was cut.
+//
+// Token shift: n_prev is the un-shifted n of the token before in the same request. For the first
+// token of a request's portion it is read from the request's state slot (`prev`, zeros for a fresh
+// request); for any other it is computed again from the row before. The last token of a portion
+// leaves its n in `last` [requests, D], and the block's *leave* kernel copies that into the slot:
+// a portion's first token reads the slot while its last one would write it, so the write waits
+// for the next kernel.
+#include "common.cuh"
+
+#define OMNIA_MAX_STREAMS 8
+
+// The request of token t: the last s with cu_seqlens[s] <= t.
+__device__ __forceinline__ int request_of(const int* __restrict__ cu_seqlens, int num_seqs, int t) {
+  int lo = 0, hi = num_seqs - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_seqlens[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+template <typename T>
+__global__ void streams_enter_kernel(const float* __restrict__ xs, const float* __restrict__ coef, int S, int D,
+                                     const float* __restrict__ w, float eps, int groups,
+                                     const float* __restrict__ mu, const float* __restrict__ prev,
+                                     float* __restrict__ last, const int* __restrict__ cu_seqlens,
+                                     const int* __restrict__ state_slots, int num_seqs, T* __restrict__ h,
+                                     float* __restrict__ sum_out) {
+  pdl_wait();
+  pdl_launch_dependents();
+  extern __shared__ float rows[];  // u of this token [D], u of the token before [D]
+  __shared__ float part[2][32];
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float a[OMNIA_MAX_STREAMS];
+#pragma unroll
+  for (int s = 0; s < OMNIA_MAX_STREAMS; ++s) a[s] = s < S ? (coef ? coef[s] : 1.f) : 0.f;
+
+  int seq = 0, from_state = 0, is_last = 0;
+  if (mu != nullptr) {
+    seq = request_of(cu_seqlens, num_seqs, t);
+    from_state = t == cu_seqlens[seq];
+    is_last = t + 1 == cu_seqlens[seq + 1];
+  }
+  const bool again = mu != nullptr && !from_state;  // the row before is normed again
+  float* u0 = rows;
+  float* u1 = rows + D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = 0.f, p = 0.f;
+    for (int s = 0; s < S; ++s) {
+      v += a[s] * xs[((size_t)t * S + s) * D + i];
+      if (again) p += a[s] * xs[((size_t)(t - 1) * S + s) * D + i];
+    }
+    u0[i] = v;
+    u1[i] = p;
+    if (sum_out != nullptr) sum_out[(size_t)t * D + i] = v;
+  }
+  __syncthreads();
+
+  // A team of W warps per group; teams take the groups in turn.
+  const int W = groups < nwarps ? nwarps / groups : 1;
+  const int teams = nwarps / W;
+  const int team = warp / W, wi = warp % W;
+  const int gs = D / groups;
+  const float* prev_row = (mu != nullptr && from_state) ? prev + (size_t)state_slots[seq] * D : nullptr;
+  for (int g0 = 0; g0 < groups; g0 += teams) {
+    const int g = g0 + team;
+    const bool active = team < teams && g < groups;
+    float s0 = 0.f, s1 = 0.f;
+    if (active) {
+      for (int i = g * gs + wi * 32 + lane; i < (g + 1) * gs; i += W * 32) {
+        s0 += u0[i] * u0[i];
+        s1 += u1[i] * u1[i];
+      }
+    }
+    s0 = warp_sum(s0);
+    s1 = warp_sum(s1);
+    __syncthreads();
+    if (lane == 0) part[0][warp] = s0, part[1][warp] = s1;
+    __syncthreads();
+    if (!active) continue;
+    float t0 = 0.f, t1 = 0.f;
+    for (int j = 0; j < W; ++j) t0 += part[0][team * W + j], t1 += part[1][team * W + j];
+    const float r0 = rsqrtf(t0 / (float)gs + eps), r1 = rsqrtf(t1 / (float)gs + eps);
+    for (int i = g * gs + wi * 32 + lane; i < (g + 1) * gs; i += W * 32) {
+      const float n = u0[i] * r0 * w[i];
+      float out = n;
+      if (mu != nullptr) {
+        const float before = from_state ? prev_row[i] : u1[i] * r1 * w[i];
+        out = n + (before - n) * mu[i];
+        if (is_last) last[(size_t)seq * D + i] = n;
+      }
+      h[(size_t)t * D + i] = from_f32<T>(out);
+    }
+  }
+}
+
+extern "C" int omnia_streams_enter(const float* xs, const float* coef, int streams, int width, const float* w,
+                                   float eps, int groups, const float* mu, const float* prev, float* last,
+                                   const int* cu_seqlens, const int* state_slots, int num_seqs, void* h,
+                                   float* sum_out, int tokens, int dtype, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (streams < 1 || streams > OMNIA_MAX_STREAMS || groups < 1 || width % groups != 0) return (int)cudaErrorInvalidValue;
+  const size_t smem = 2 * sizeof(float) * (size_t)width;
+  OMNIA_DISPATCH_DTYPE(dtype, {
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(streams_enter_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return (int)cudaGetLastError();
+    launch_pdl(streams_enter_kernel<T>, tokens, 256, smem, stream, xs, coef, streams, width, w, eps, groups, mu, prev,
+               last, cu_seqlens, state_slots, num_seqs, (T*)h, sum_out);
+  });
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// Blocks 0 .. tokens-1 update a token's streams; blocks tokens .. tokens+commits-1 copy a
+// request's `last` row into its state slot (see the top of the file).
+template <typename T>
+__global__ void streams_leave_kernel(float* __restrict__ xs, const T* __restrict__ y, const float* __restrict__ mix,
+                                     const float* __restrict__ outc, int S, int D, int tokens,
+                                     const float* __restrict__ last, float* __restrict__ prev,
+                                     const int* __restrict__ state_slots) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  if (t >= tokens) {
+    const int seq = t - tokens;
+    float* to = prev + (size_t)state_slots[seq] * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) to[i] = last[(size_t)seq * D + i];
+    return;
+  }
+  __shared__ float m[OMNIA_MAX_STREAMS * OMNIA_MAX_STREAMS + OMNIA_MAX_STREAMS];
+  if (threadIdx.x < S * S) m[threadIdx.x] = mix ? mix[threadIdx.x] : 1.f;
+  if (threadIdx.x < S) m[OMNIA_MAX_STREAMS * OMNIA_MAX_STREAMS + threadIdx.x] = outc ? outc[threadIdx.x] : 1.f;
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float old[OMNIA_MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < OMNIA_MAX_STREAMS; ++s)
+      if (s < S) old[s] = xs[((size_t)t * S + s) * D + i];
+    const float branch = to_f32(y[(size_t)t * D + i]);
+#pragma unroll
+    for (int to = 0; to < OMNIA_MAX_STREAMS; ++to) {
+      if (to >= S) break;
+      float v = 0.f;
+#pragma unroll
+      for (int s = 0; s < OMNIA_MAX_STREAMS; ++s)
+        if (s < S) v += m[s * S + to] * old[s];
+      xs[((size_t)t * S + to) * D + i] = v + m[OMNIA_MAX_STREAMS * OMNIA_MAX_STREAMS + to] * branch;
+    }
+  }
+}
+
+extern "C" int omnia_streams_leave(float* xs, const void* y, const float* mix, const float* outc, int streams,
+                                   int width, int tokens, const float* last, float* prev, const int* state_slots,
+                                   int commits, int dtype, cudaStream_t stream) {
+  if (tokens + commits == 0) return 0;
+  if (streams < 1 || streams > OMNIA_MAX_STREAMS || (mix == nullptr && streams != 1)) return (int)cudaErrorInvalidValue;
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(streams_leave_kernel<T>, tokens + commits, 256, 0, stream, xs, (const T*)y,
+                                          mix, outc, streams, width, tokens, last, prev, state_slots)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// x_s = table[id] * multiplier for every stream s: the residual streams at their start.
+template <typename T>
+__global__ void embed_streams_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ xs,
+                                     int S, int D, int vocab, float multiplier, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, OMNIA_ERR_TOKEN_ID);
+    id = 0;
+  }
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float v = to_f32(table[(size_t)id * D + i]) * multiplier;
+    for (int s = 0; s < S; ++s) xs[((size_t)t * S + s) * D + i] = v;
+  }
+}
+
+extern "C" int omnia_embed_streams(const int* ids, const void* table, float* xs, int tokens, int streams, int width,
+                                   int vocab, float multiplier, int dtype, int* err, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(embed_streams_kernel<T>, tokens, 256, 0, stream, ids, (const T*)table, xs,
+                                          streams, width, vocab, multiplier, err)));
+  return OMNIA_LAUNCH_RESULT();
+}

@@ -153,7 +153,7 @@ class DecodeGraphs:
         runner = self.runner
         starts = runner.take_pages(entries)
         batch = _bucket(len(entries))
-        width = ops.width_bucket(max(max(len(t) for t in e.request.tables) for e in entries))
+        width = ops.width_bucket(max(max((len(t) for t in e.request.tables), default=0) for e in entries))
         captured = self._graph_for(batch, width)
         if captured.copied is not None:
             captured.copied.synchronize()  # the pinned buffer is free to be written again

@@ -15,7 +15,7 @@ from mlx_omnia_b200.kernels import ops
 from mlx_omnia_b200.parts.base import Runtime
 from mlx_omnia_b200.parts.model import DecoderModel, ModelSpec
 from mlx_omnia_b200.registry import Architecture, resolve_architecture
-from mlx_omnia_b200.weights.loader import load_tensors
+from mlx_omnia_b200.weights.loader import load_tensors, open_source
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -105,6 +105,10 @@ class Engine:
         args = args or EngineArgs()
         architecture = resolve_architecture(raw_config)
         config = architecture.parse(raw_config)
+        source = open_source(source)
+        if architecture.sizes_from_tensors is not None:
+            held = set(source.names())
+            config = architecture.sizes_from_tensors(config, lambda name: source.shape(name) if name in held else None)
         runtime = _runtime(args)
         model = DecoderModel(spec if spec is not None else architecture.model_spec(config))
         model.load(load_tensors(source, architecture, config, model.tensors(), runtime), runtime)

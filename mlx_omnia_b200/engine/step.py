@@ -182,7 +182,8 @@ class StepRunner:
                 table, slots = step.groups[g]
                 kv = KVView(cache.entry_pages(entry), table, slots, cache.page_size, cache.groups[g].spec.window,
                             writes=need.reads is None, spec=cache.groups[g].spec)
-            contexts.append(LayerContext(step, kv, cache.state.get(entry), entry))
+            contexts.append(LayerContext(step, kv, cache.state.get(entry), entry,
+                                         block_state=cache.block_state.get(entry)))
         return contexts
 
     # -- the step ----------------------------------------------------------------------
@@ -192,15 +193,7 @@ class StepRunner:
         graph's own logits buffer, which the next step overwrites. `device_tokens`
         (int32 on the device, one per entry; graph steps only) are the step's tokens when
         the host does not know them yet."""
-        fresh_slots = [e.request.slot for e in entries if e.request.fresh]
-        if fresh_slots and self.cache.state:
-            index = torch.as_tensor(fresh_slots, device=self.runtime.device)
-            for entry, state in self.cache.state.items():
-                initial = self.cache.initial_state.get(entry)
-                if initial is None:
-                    state.index_fill_(0, index, 0)
-                else:
-                    state[index] = initial
+        self.cache.reset_slots([e.request.slot for e in entries if e.request.fresh])
         if self.graphs is not None and entries and all(len(e.tokens) == 1 and e.want in ([], [0]) for e in entries):
             logits = self.graphs.run(entries, copy, device_tokens)
         else:

@@ -935,3 +935,173 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
               _ptr(penalty), _ptr(history), 0 if history is None else history.shape[1], _ptr(seeds), _ptr(draws),
               _ptr(out), _stream()), "sample")
     return out
+
+
+# ------------------------------------------------------------------------------------
+# Residual streams, grouped norm and token shift (csrc/streams.cu)
+
+MAX_STREAMS = 8
+
+
+def embed_streams(ids: torch.Tensor, table: torch.Tensor, multiplier: float, streams: int) -> torch.Tensor:
+    """x[t, s] = table[ids[t]] * multiplier for each of `streams` copies -> float32 [tokens, streams * hidden]."""
+    tokens, (vocab, hidden) = ids.shape[0], table.shape
+    x = torch.empty(tokens, streams * hidden, dtype=torch.float32, device=table.device)
+    fn = _function("streams", "omnia_embed_streams",
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(ids), _ptr(table), _ptr(x), tokens, streams, hidden, vocab, multiplier, _code(table.dtype),
+              _ptr(error_word(table.device)), _stream()), "embed_streams")
+    return x
+
+
+def streams_enter(xs: torch.Tensor, coef: torch.Tensor | None, streams: int, weight: torch.Tensor, eps: float,
+                  groups: int, dtype: torch.dtype, step: StepContext | None = None, shift: torch.Tensor | None = None,
+                  prev: torch.Tensor | None = None, last: torch.Tensor | None = None,
+                  total: torch.Tensor | None = None) -> torch.Tensor:
+    """h = norm(sum_s coef[s] xs[:, s]) with the RMS taken over `groups` equal runs of the width, then
+    (with `shift`) h + (h_before - h) * shift, h_before being the token before's normed row: read from
+    `prev` [slots, width] (by the step's state slots) for the first token of a request's portion. The
+    last token of each portion leaves its normed row in `last` [requests, width] (float32), which
+    `streams_leave` commits to `prev`. xs float32 [tokens, streams * width]; coef None means ones.
+    `total` (float32 [tokens, width]), when given, receives the weighted sum of the streams itself."""
+    tokens, width = xs.shape[0], xs.shape[1] // streams
+    h = torch.empty(tokens, width, dtype=dtype, device=xs.device)
+    fn = _function("streams", "omnia_streams_enter",
+                   [c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                    c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    shifted = shift is not None
+    _check(fn(_ptr(xs), _ptr(coef), streams, width, _ptr(weight), eps, groups, _ptr(shift),
+              _ptr(prev) if shifted else None, _ptr(last) if shifted else None,
+              _ptr(step.cu_seqlens) if shifted else None, _ptr(step.state_slots) if shifted else None,
+              step.num_seqs if shifted else 0, _ptr(h), _ptr(total), tokens, _code(dtype), _stream()), "streams_enter")
+    return h
+
+
+def streams_leave(xs: torch.Tensor, branch: torch.Tensor, mix: torch.Tensor | None, out: torch.Tensor | None,
+                  streams: int, step: StepContext | None = None, last: torch.Tensor | None = None,
+                  prev: torch.Tensor | None = None) -> None:
+    """In place: xs[:, t] = sum_s mix[s, t] xs[:, s] + out[t] * branch for all t at once (`mix` None with
+    one stream: xs += branch). With `last` and `prev`, every request's row of `last` is also copied
+    into its state slot of `prev` (the token shift's commit)."""
+    tokens, width = xs.shape[0], xs.shape[1] // streams
+    commits = step.num_seqs if last is not None else 0
+    fn = _function("streams", "omnia_streams_leave",
+                   [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                    c_int, c_void_p])
+    _check(fn(_ptr(xs), _ptr(branch), _ptr(mix), _ptr(out), streams, width, tokens, _ptr(last), _ptr(prev),
+              _ptr(step.state_slots) if commits else None, commits, _code(branch.dtype), _stream()), "streams_leave")
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(z: torch.Tensor, kind: str) -> torch.Tensor:
+    """relu(z)^2, the tanh form of GELU, or SiLU, element by element in float32."""
+    act = torch.empty_like(z)
+    fn = _function("elementwise", "omnia_activation", [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p])
+    _check(fn(_ptr(z), _ptr(act), z.numel(), ACTIVATIONS[kind], _code(z.dtype), _stream()), "activation")
+    return act
+
+
+# ------------------------------------------------------------------------------------
+# The gated delta rule and its short convolution (csrc/delta_rule.cu)
+
+MAX_CONV_TAPS = 16
+
+
+def short_conv(proj: torch.Tensor, col0: int, channels: int, taps: torch.Tensor, state: torch.Tensor,
+               step: StepContext, unit_channels: int, unit_dim: int, unit_eps: float, scaled_channels: int,
+               scale: float) -> torch.Tensor:
+    """silu(causal depth-wise convolution) of columns [col0, col0 + channels) of the projected rows,
+    the inputs before a portion read from `state` [slots, taps - 1, channels]; the first
+    `unit_channels` outputs are made unit vectors in runs of `unit_dim`, the first `scaled_channels`
+    of those also multiplied by `scale`. -> float32 [tokens, channels]. The state is not moved on
+    here (`delta_rule` does that)."""
+    tokens = proj.shape[0]
+    y = torch.empty(tokens, channels, dtype=torch.float32, device=proj.device)
+    fn = _function("delta_rule", "omnia_short_conv",
+                   [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                    c_float, c_int, c_float, c_void_p, c_int, c_int, c_void_p], {"DELTA_DK": unit_dim})
+    _check(fn(_ptr(proj), proj.shape[1], col0, channels, taps.shape[1], _ptr(taps), _ptr(state), _ptr(step.cu_seqlens),
+              _ptr(step.state_slots), step.num_seqs, unit_channels, unit_dim, unit_eps, scaled_channels, scale,
+              _ptr(y), tokens, _code(proj.dtype), _stream()), "short_conv")
+    return y
+
+
+def delta_rule(conv: torch.Tensor, groups: int, heads: int, dk: int, dv: int, proj: torch.Tensor, in_col: int,
+               beta_col: int, a_rows: torch.Tensor, gate_rows: torch.Tensor, A_log: torch.Tensor,
+               dt_bias: torch.Tensor, norm_weight: torch.Tensor, eps: float, S: torch.Tensor,
+               conv_state: torch.Tensor, taps: int, step: StepContext) -> torch.Tensor:
+    """The gated delta rule with a decay per head and key channel over this step's tokens, request by
+    request from the state in `S` [slots, heads, dk, dv] (float32, updated in place), followed by the
+    RMS norm of each head's output, its weight and the sigmoid gate. Also moves `conv_state` on by
+    this step's raw convolution inputs (columns from `in_col` of `proj`). -> [tokens, heads * dv]"""
+    tokens = proj.shape[0]
+    out = torch.empty(tokens, heads * dv, dtype=proj.dtype, device=proj.device)
+    defines = {"DELTA_DK": dk}
+    fn = _function("delta_rule", "omnia_delta_rule",
+                   [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                    c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                    c_int, c_void_p, c_int, c_void_p], defines)
+    _check(fn(_ptr(conv), conv.shape[1], groups, heads, dv, _ptr(proj), proj.shape[1], in_col, beta_col,
+              _ptr(a_rows), a_rows.shape[1], _ptr(gate_rows), gate_rows.shape[1], _ptr(A_log), _ptr(dt_bias),
+              _ptr(norm_weight), eps, _ptr(S), _ptr(conv_state), taps, _ptr(step.cu_seqlens),
+              _ptr(step.state_slots), step.num_seqs, _ptr(out), _code(proj.dtype), _stream()), "delta_rule")
+    return out
+
+
+# ------------------------------------------------------------------------------------
+# Attention over a latent cache (csrc/attention_latent.cu)
+
+LATENT_MAX_RANK = 512
+
+
+def latent_prepare(proj: torch.Tensor, q_col: int, heads: int, q_dim: int, down_col: int, rank: int, rot: int,
+                   weight: torch.Tensor, eps: float, inv_freq: torch.Tensor, positions: torch.Tensor,
+                   kv: KVView) -> None:
+    """Per projected row: the RMS-normed latent (columns [down_col, down_col + rank)) and the rotated
+    shared key part (the `rot` columns after it) go to the row's cache slot; the last `rot` dims of
+    each of the `heads` query heads (each `q_dim` wide, from `q_col`) are rotated in place. The rotation
+    pairs dims (2i, 2i + 1) over the first 2 * len(inv_freq) of the `rot`."""
+    store = kv.writes
+    fn = _function("attention_latent", "omnia_latent_prepare",
+                   [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int,
+                    c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(proj), proj.shape[1], q_col, heads, q_dim, down_col, rank, rot, _ptr(weight), eps, _ptr(inv_freq),
+              2 * inv_freq.shape[0], _ptr(positions), _ptr(kv.slot_mapping) if store else None, _ptr(kv.pages),
+              kv.pages.shape[0] * kv.page_size, proj.shape[0], _code(proj.dtype), _ptr(error_word(proj.device)),
+              _stream()), "latent_prepare")
+
+
+def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, kv: KVView, step: StepContext, scale: float,
+                     sink: torch.Tensor | None, gate: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:
+    """Causal attention of every head over the cache's latent rows (see csrc/attention_latent.cu).
+    q_lat [heads, tokens, rank], q_rot [tokens, heads, rot] and out [heads, tokens, rank] may be
+    strided views (last dim contiguous); gate [tokens, >= heads] holds one logit per head in its
+    first columns; sink float32 [heads]."""
+    heads, tokens, rank = q_lat.shape
+    rot = q_rot.shape[2]
+    if q_lat.stride(2) != 1 or q_rot.stride(2) != 1 or out.stride(2) != 1 or (gate is not None and gate.stride(1) != 1):
+        raise KernelError("latent_attention wants the last dim of its operands contiguous")
+    if rank > LATENT_MAX_RANK:
+        raise KernelError(f"latent_attention takes a latent of at most {LATENT_MAX_RANK}, got {rank}")
+    fn = _function("attention_latent", "omnia_latent_attention",
+                   [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
+                    c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_int,
+                    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(1), q_rot.stride(0),
+              _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.positions), _ptr(sink),
+              _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), out.stride(0), out.stride(1), tokens,
+              step.num_seqs, kv.block_table.shape[1], kv.pages.shape[0], heads, rank, rot, kv.page_size,
+              kv.window or 0, scale, _code(q_lat.dtype), _ptr(error_word(q_lat.device)), _stream()),
+           "latent_attention")
+    return out
+
+
+def batched_mm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """a [batch, rows, k] times b [batch, k, n] -> [batch, rows, n]: the vendor library's strided
+    batched product (float32 accumulation; true float32 on the 32-bit path)."""
+    if a.dtype == torch.float32 and (torch.backends.cuda.matmul.allow_tf32
+                                      or torch.get_float32_matmul_precision() != "highest"):
+        raise KernelError("the 32-bit path needs true float32 matrix products; TF32 is switched on")
+    return torch.bmm(a, b) if out is None else torch.bmm(a, b, out=out)

@@ -42,6 +42,8 @@ class GQAAttention(Mixer):
         self.hidden, self.heads, self.kv_heads, self.head_dim = hidden, heads, kv_heads, head_dim
         self.scale, self.window, self.qk_norm_eps, self.gated, self.own_kv = scale, window, qk_norm_eps, gated, own_kv
         self.position = POSITIONS.build(position or PartSpec("none"))
+        if getattr(self.position, "pairing", "half") != "half":
+            raise ValueError("gqa_attention rotates half-split pairs")
 
     def kv_spec(self) -> KVSpec:
         return KVSpec.keys_and_values(self.kv_heads, self.head_dim, self.window)
@@ -103,3 +105,92 @@ class GQAAttention(Mixer):
                                        ctx.kv if self.own_kv else None)
             out = ops.paged_attention(q, ctx.kv, ctx.step, self.scale, gate=gate, gate_col=self.gate_col)
         return ops.linear(out, self.o_proj)
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    """Causal attention whose keys and values are expanded from one low-rank row per position.
+
+    hidden, heads: sizes; dim: unrotated query/key dims per head; rot_dim: rotated ones (a query head
+    is laid out [dim | rot_dim]); vdim: value dims per head; kv_rank: width of the latent.
+    The down projection gives kv_rank + rot_dim numbers per token: the first kv_rank, RMS-normed
+    (`dkv.norm`, eps `norm_eps`), are the latent c; the last rot_dim, rotated, are one key part that
+    all heads share. Head h's key is [uk_h c | shared part], its value uv_h c; only [c | shared part]
+    is cached, one row per position. This engine never expands the cache: uk is folded into the query
+    (q_lat = uk_h^T q_plain) and uv applied to the attention's output in latent space.
+    scale:    multiplies the scores
+    position: a rotary part with interleaved pairing over the first `dims` of the rot_dim
+    sink:     the softmax's denominator also holds exp(sink_h) (tensor `sink` [heads], unscaled)
+    gated:    head h's output is multiplied by sigmoid(g(h))_h (tensor `g` [heads, hidden])
+    window:   None, or how many latest positions are visible
+
+    Tensors: q [heads * (dim + rot_dim), hidden]; dkv [kv_rank + rot_dim, hidden]; dkv.norm [kv_rank];
+    uk [heads * dim, kv_rank]; uv [heads * vdim, kv_rank]; o [hidden, heads * vdim]."""
+
+    graph_safe = True
+    graph_safe_mixed = True
+
+    def __init__(self, hidden: int, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float,
+                 norm_eps: float, position: PartSpec, sink: bool = True, gated: bool = True,
+                 window: int | None = None) -> None:
+        if kv_rank > ops.LATENT_MAX_RANK:
+            raise ValueError(f"latent_attention takes a latent of at most {ops.LATENT_MAX_RANK}")
+        self.hidden, self.heads, self.dim, self.rot_dim, self.vdim, self.kv_rank = hidden, heads, dim, rot_dim, vdim, kv_rank
+        self.scale, self.norm_eps, self.sink, self.gated, self.window = float(scale), float(norm_eps), sink, gated, window
+        self.position = POSITIONS.build(position)
+        if getattr(self.position, "pairing", None) != "interleaved":
+            raise ValueError("latent_attention rotates interleaved pairs")
+        if self.position.dims > rot_dim:
+            raise ValueError(f"{self.position.dims} rotary dims do not fit a rotated part of {rot_dim}")
+
+    def kv_spec(self) -> KVSpec:
+        return KVSpec(((1, self.kv_rank + self.rot_dim),), self.window)
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        H, qd = self.heads, self.dim + self.rot_dim
+        specs = {"q": TensorSpec((H * qd, self.hidden)), "dkv": TensorSpec((self.kv_rank + self.rot_dim, self.hidden)),
+                 "dkv.norm": TensorSpec((self.kv_rank,), "vector"), "uk": TensorSpec((H * self.dim, self.kv_rank)),
+                 "uv": TensorSpec((H * self.vdim, self.kv_rank)), "o": TensorSpec((self.hidden, H * self.vdim))}
+        if self.sink:
+            specs["sink"] = TensorSpec((H,), "vector")
+        if self.gated:
+            specs["g"] = TensorSpec((H, self.hidden))
+        return specs
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        self.position.load({}, runtime)
+        H, qd = self.heads, self.dim + self.rot_dim
+        # One operand [q | down | gate] (rows padded to a multiple of 8).
+        rows = [tensors["q"], tensors["dkv"]]
+        self.down_col = H * qd
+        self.gate_col = self.down_col + self.kv_rank + self.rot_dim
+        total = self.gate_col
+        if self.gated:
+            rows.append(tensors["g"])
+            total += H
+        if total % 8:
+            rows.append(torch.zeros(8 - total % 8, self.hidden, dtype=rows[0].dtype, device=rows[0].device))
+        self.in_proj = torch.cat(rows, dim=0).contiguous()
+        self.down_norm = tensors["dkv.norm"].contiguous()
+        self.uk = tensors["uk"].view(H, self.dim, self.kv_rank).contiguous()  # q_lat = q_plain @ uk_h
+        self.uv_t = tensors["uv"].view(H, self.vdim, self.kv_rank).transpose(1, 2).contiguous()  # [H, rank, vdim]
+        self.o = tensors["o"].contiguous()
+        self.sink_logits = tensors["sink"].contiguous() if self.sink else None
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        if ctx.kv is None:
+            raise RuntimeError("an attention mixer needs cache pages")
+        H, qd, step = self.heads, self.dim + self.rot_dim, ctx.step
+        proj = ops.linear(h, self.in_proj)
+        tokens = proj.shape[0]
+        ops.latent_prepare(proj, 0, H, qd, self.down_col, self.kv_rank, self.rot_dim, self.down_norm, self.norm_eps,
+                           self.position.table(), step.positions, ctx.kv)
+        q = proj[:, : H * qd].view(tokens, H, qd)
+        q_lat = ops.batched_mm(q[:, :, : self.dim].transpose(0, 1), self.uk)  # [H, tokens, rank]
+        o_lat = torch.empty(H, tokens, self.kv_rank, dtype=proj.dtype, device=proj.device)
+        ops.latent_attention(q_lat, q[:, :, self.dim:], ctx.kv, step, self.scale, self.sink_logits,
+                             proj[:, self.gate_col:] if self.gated else None, o_lat)
+        out = torch.empty(tokens, H, self.vdim, dtype=proj.dtype, device=proj.device)
+        ops.batched_mm(o_lat, self.uv_t, out=out.transpose(0, 1))
+        return ops.linear(out.view(tokens, H * self.vdim), self.o)

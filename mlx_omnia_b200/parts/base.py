@@ -16,8 +16,10 @@ Mixer additionally (class attributes `graph_safe` / `graph_safe_mixed`: its forw
 host-side work per request in a step of single tokens / in any step, so such steps may be
 captured into CUDA graphs):
     ``kv_spec() -> KVSpec | None``              rows it keeps per position, in pages
-    ``state_spec() -> StateSpec | None``        fixed-size state it keeps per request
-    ``initial_state() -> Tensor | None``        what that state starts as (None: zeros)
+    ``state_spec() -> StateSpec | {name: StateSpec} | None``  fixed-size state it keeps per request
+                                                (several named tensors when it gives a dict)
+    ``initial_state() -> Tensor | None``        what a single state tensor starts as (None: zeros;
+                                                named state always starts as zeros)
     ``forward(h, ctx: LayerContext) -> branch`` h, branch: [tokens, hidden] engine dtype
 FeedForward:  ``forward(h, ctx) -> branch``
               A mixer or feed-forward whose `forward` gives `h` to one ``ops.linear`` or
@@ -27,7 +29,10 @@ Norm:         ``forward(x) -> h`` and the attributes ``weight``, ``eps`` that th
               fused residual kernel reads (``weight is None`` means weightless)
 Position:     ``table() -> float32[rotary_dims / 2] | None`` of inverse frequencies
 Embedding:    ``forward(token_ids, positions) -> x`` float32 [tokens, hidden]
-Block:        ``entry_norm`` and ``forward(x, h, ctx, exit_norm) -> (x, h_next)``
+Block:        ``entry_norm`` and ``forward(x, h, ctx, exit_norm) -> (x, h_next)``; a block whose
+              ``entry_norm`` is None does its own entry from the residual it is handed (`h` is then
+              None, and the block before it is given no exit norm); ``state_spec()`` may give named
+              per-request state of the block's own (``ctx.block_state``), beside its mixer's
 """
 
 from __future__ import annotations
@@ -127,7 +132,7 @@ class Mixer(Part):
     def kv_spec(self) -> KVSpec | None:
         return None
 
-    def state_spec(self) -> StateSpec | None:
+    def state_spec(self) -> "StateSpec | dict[str, StateSpec] | None":
         return None
 
     def initial_state(self) -> torch.Tensor | None:
@@ -170,6 +175,10 @@ class Embedding(Part):
 
 class Block(Part):
     entry_norm: Norm | None = None
+
+    def state_spec(self) -> "dict[str, StateSpec] | None":
+        """Named per-request state of the block itself (zeros at a request's start)."""
+        return None
 
     def forward(self, x, h, ctx: "LayerContext", exit_norm: Norm | None):  # pragma: no cover
         raise NotImplementedError
@@ -300,6 +309,7 @@ class LayerContext:
 
     step: StepContext
     kv: KVView | None
-    state: torch.Tensor | None  # [num_slots, *StateSpec.shape]
+    state: "torch.Tensor | dict[str, torch.Tensor] | None"  # [num_slots, *StateSpec.shape], by name if so declared
     entry: int
+    block_state: "dict[str, torch.Tensor] | None" = None  # the block's own named state
     exit_may_pend: bool = False  # whatever takes this entry's h takes a pending residual step too

@@ -18,7 +18,7 @@ from __future__ import annotations
 import torch
 
 from mlx_omnia_b200.kernels import ops
-from mlx_omnia_b200.parts.base import (FEED_FORWARDS, MIXERS, NORMS, Block, Norm, PartSpec, TensorSpec,
+from mlx_omnia_b200.parts.base import (FEED_FORWARDS, MIXERS, NORMS, Block, Norm, PartSpec, StateSpec, TensorSpec,
                                        register_block)
 from mlx_omnia_b200.parts.norms import RMSNorm
 
@@ -29,8 +29,8 @@ def residual_step(x: torch.Tensor, branch: torch.Tensor, branch_norm: Norm | Non
     RMS norms take the fused kernel; any other norm class is applied by its own forward.
     With `may_pend` (whoever takes the result says it `takes_pending`) a step of few rows is
     not run here but handed on as an `ops.PendingStep`, for the taker's first product to run."""
-    fused_b = branch_norm is None or isinstance(branch_norm, RMSNorm)
-    fused_o = out_norm is None or isinstance(out_norm, RMSNorm)
+    fused_b = branch_norm is None or (isinstance(branch_norm, RMSNorm) and branch_norm.groups == 1)
+    fused_o = out_norm is None or (isinstance(out_norm, RMSNorm) and out_norm.groups == 1)
     if may_pend and fused_b and fused_o and out_norm is not None and ops.pending_supported(x, branch):
         return ops.PendingStep(x, branch, None if branch_norm is None else branch_norm.weight,
                                None if branch_norm is None else branch_norm.eps, out_norm.weight, out_norm.eps)
@@ -113,3 +113,103 @@ class PreNormBlock(_TwoBranchBlock):
         m = self.feed_forward.forward(h2, ctx)
         x = ops.residual_after(h2, x)
         return x, residual_step(x, m, None, exit_norm, ctx.exit_may_pend)
+
+
+@register_block("hyper_pre_norm")
+class HyperPreNormBlock(Block):
+    """A pre-norm block whose residual may be several streams, whose mixer may read a token-shifted
+    input, and whose feed-forward may be missing.
+
+    hidden:       the model width
+    mixer:        PartSpec of the mixer; feed_forward: PartSpec or None (the block then has one branch)
+    norms:        {"norm1": spec, "norm2": spec} of `rms_norm` parts (grouped or not); norm2 only with
+                  a feed-forward
+    streams:      None for the ordinary residual x += branch. n >= 1 keeps n residual streams
+                  x_1..x_n side by side ([tokens, n * hidden]); branch q (1 mixer, 2 feed-forward) reads
+                  u = sum_s in_q[s] x_s and is written back as x_t = sum_s mix_q[s, t] x_s + out_q[t] y for
+                  all t at once (tensors `hc<q>.in` [n], `hc<q>.out` [n], `hc<q>.mix` [n, n], from-stream
+                  first). The embedding writes the n equal copies the streams start as.
+    shift:        the mixer reads h + (h_before - h) * mu instead of its normed input h, with h_before
+                  the normed input of the token before (zeros ahead of the first token) and mu the
+                  tensor `shift` [hidden]; h_before of a request's last token is kept in a state slot.
+
+    The block does its own entry (`entry_norm` is None). Given an exit norm (whatever follows is
+    not a block of this kind: the model's final norm) it hands on the sum of the streams, normed."""
+
+    entry_norm = None
+
+    def __init__(self, hidden: int, mixer: PartSpec, feed_forward: PartSpec | None, norms: dict[str, PartSpec],
+                 streams: int | None = None, shift: bool = False, mixer_name: str = "mix",
+                 feed_forward_name: str = "mlp") -> None:
+        if streams is not None and not 1 <= streams <= ops.MAX_STREAMS:
+            raise ValueError(f"a residual of {streams} streams (at most {ops.MAX_STREAMS})")
+        self.hidden, self.streams, self.shift = hidden, streams, shift
+        self.mixer = MIXERS.build(mixer)
+        self.feed_forward = FEED_FORWARDS.build(feed_forward) if feed_forward is not None else None
+        wanted = ("norm1", "norm2") if feed_forward is not None else ("norm1",)
+        if set(wanted) - set(norms):
+            raise ValueError(f"hyper_pre_norm needs the norms {wanted}")
+        self.norms = {name: NORMS.build(norms[name]) for name in wanted}
+        for name, norm in self.norms.items():
+            if not isinstance(norm, RMSNorm) or norm.convention == "none":
+                raise ValueError(f"hyper_pre_norm's {name} must be an rms_norm with a weight")
+        self.mixer_name, self.feed_forward_name = mixer_name, feed_forward_name
+
+    def children(self):
+        yield self.mixer_name, self.mixer
+        if self.feed_forward is not None:
+            yield self.feed_forward_name, self.feed_forward
+        yield from self.norms.items()
+
+    def branches(self) -> list[str]:
+        return ["hc1", "hc2"] if self.feed_forward is not None else ["hc1"]
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        specs = {f"{name}.{local}": spec for name, part in self.children() for local, spec in part.tensors().items()}
+        if self.streams is not None:
+            n = self.streams
+            for hc in self.branches():
+                specs.update({f"{hc}.in": TensorSpec((n,), "vector"), f"{hc}.out": TensorSpec((n,), "vector"),
+                              f"{hc}.mix": TensorSpec((n, n), "vector")})
+        if self.shift:
+            specs["shift"] = TensorSpec((self.hidden,), "vector")
+        return specs
+
+    def state_spec(self):
+        return {"shift": StateSpec((self.hidden,), torch.float32)} if self.shift else None
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        for name, part in self.children():
+            prefix = name + "."
+            part.load({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, runtime)
+        self.hc = {hc: tuple(tensors[f"{hc}.{which}"].contiguous() for which in ("in", "mix", "out"))
+                   if self.streams is not None else (None, None, None) for hc in self.branches()}
+        self.mu = tensors["shift"].contiguous() if self.shift else None
+
+    def forward(self, x, h, ctx, exit_norm):
+        n = self.streams or 1
+        if x.shape[1] != n * self.hidden:
+            raise RuntimeError(f"a residual of {n} streams of {self.hidden} was handed {x.shape[1]} columns")
+        dtype, step = self.runtime.dtype, ctx.step
+        norm = self.norms["norm1"]
+        a_in, a_mix, a_out = self.hc["hc1"]
+        prev = last = None
+        if self.shift:
+            prev = ctx.block_state["shift"]
+            last = torch.empty(step.num_seqs, self.hidden, dtype=torch.float32, device=x.device)
+        h1 = ops.streams_enter(x, a_in, n, norm.weight, norm.eps, norm.groups, dtype, step, self.mu, prev, last)
+        ops.streams_leave(x, self.mixer.forward(h1, ctx), a_mix, a_out, n, step, last, prev)
+        if self.feed_forward is not None:
+            norm = self.norms["norm2"]
+            b_in, b_mix, b_out = self.hc["hc2"]
+            h2 = ops.streams_enter(x, b_in, n, norm.weight, norm.eps, norm.groups, dtype)
+            ops.streams_leave(x, self.feed_forward.forward(h2, ctx), b_mix, b_out, n)
+        if exit_norm is None:
+            return x, None
+        if isinstance(exit_norm, RMSNorm) and exit_norm.convention != "none":
+            total = torch.empty(x.shape[0], self.hidden, dtype=torch.float32, device=x.device)
+            out = ops.streams_enter(x, None, n, exit_norm.weight, exit_norm.eps, exit_norm.groups, dtype, total=total)
+            return total, out
+        total = x.view(x.shape[0], n, self.hidden).sum(1) if n > 1 else x
+        return total, exit_norm.forward(total)

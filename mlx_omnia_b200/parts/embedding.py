@@ -18,11 +18,15 @@ from mlx_omnia_b200.parts.base import Embedding, Part, TensorSpec, register_embe
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Embedding):
-    """x = table[ids], RMS-normalised without a weight when `norm_eps` is given.
-    The output is the float32 residual stream."""
+    """x = table[ids], RMS-normalised without a weight when `norm_eps` is given, or multiplied by
+    `scale`; with `copies` n the row is written n times side by side (the start of a residual
+    kept as n streams). The output is the float32 residual stream."""
 
-    def __init__(self, vocab: int, hidden: int, norm_eps: float | None = None) -> None:
-        self.vocab, self.hidden, self.norm_eps = vocab, hidden, norm_eps
+    def __init__(self, vocab: int, hidden: int, norm_eps: float | None = None, scale: float = 1.0,
+                 copies: int = 1) -> None:
+        if norm_eps is not None and (scale != 1.0 or copies != 1):
+            raise ValueError("a normed embedding is neither scaled nor copied")
+        self.vocab, self.hidden, self.norm_eps, self.scale, self.copies = vocab, hidden, norm_eps, float(scale), copies
 
     def tensors(self) -> dict[str, TensorSpec]:
         return {"weight": TensorSpec((self.vocab, self.hidden))}
@@ -32,6 +36,8 @@ class TokenEmbedding(Embedding):
         self.weight = tensors["weight"].contiguous()
 
     def forward(self, token_ids: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
+        if self.scale != 1.0 or self.copies != 1:
+            return ops.embed_streams(token_ids, self.weight, self.scale, self.copies)
         return ops.embed_rmsnorm(token_ids, self.weight, self.norm_eps)
 
 

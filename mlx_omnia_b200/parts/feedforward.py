@@ -39,3 +39,27 @@ class GatedMLP(FeedForward):
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         return ops.linear(ops.linear_swiglu(h, self.gate_up), self.down)
+
+
+@register_feed_forward("dense_mlp")
+class DenseMLP(FeedForward):
+    """down(act(up(h))), no biases and no gate.
+
+    hidden, inner: widths; activation: "relu2" (the square of relu), "gelu_tanh" or "silu".
+    Tensors: `up` [inner, hidden], `down` [hidden, inner].
+    """
+
+    def __init__(self, hidden: int, inner: int, activation: str = "relu2") -> None:
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"dense_mlp activation {activation!r}; known: {sorted(ops.ACTIVATIONS)}")
+        self.hidden, self.inner, self.activation = hidden, inner, activation
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {"up": TensorSpec((self.inner, self.hidden)), "down": TensorSpec((self.hidden, self.inner))}
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        self.up, self.down = tensors["up"].contiguous(), tensors["down"].contiguous()
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        return ops.linear(ops.activation(ops.linear(h, self.up), self.activation), self.down)

@@ -60,9 +60,10 @@ class CacheNeed:
     """What one schedule entry asks of the cache manager."""
 
     kv: KVSpec | None  # pages it owns (None: none, or it reads another entry's)
-    state: StateSpec | None
+    state: "StateSpec | dict[str, StateSpec] | None"  # the mixer's
     reads: int | None
     initial_state: torch.Tensor | None = None  # what a request's state starts as (None: zeros)
+    block_state: "dict[str, StateSpec] | None" = None  # the block's own
 
 
 class DecoderModel:
@@ -106,7 +107,8 @@ class DecoderModel:
                 if kv != owner:
                     raise ValueError(f"a schedule entry reads a cache of {owner} but its mixer keeps {kv}")
                 kv = None
-            needs.append(CacheNeed(kv, state, entry.reads, mixer.initial_state() if state is not None else None))
+            needs.append(CacheNeed(kv, state, entry.reads, mixer.initial_state() if state is not None else None,
+                                   self.blocks[entry.layer].state_spec()))
         return needs
 
     # -- the step --------------------------------------------------------------------
@@ -115,7 +117,8 @@ class DecoderModel:
         schedule = self.spec.schedule
         ops.begin_pass(step)
         x = self.embedding.forward(step.token_ids, step.positions)
-        h = self.blocks[schedule[0].layer].entry_norm.forward(x)
+        first = self.blocks[schedule[0].layer].entry_norm
+        h = first.forward(x) if first is not None else None  # None: the block does its own entry
         for e, entry in enumerate(schedule):
             after = self.blocks[schedule[e + 1].layer] if e + 1 < len(schedule) else None
             following = after.entry_norm if after is not None else self.final_norm

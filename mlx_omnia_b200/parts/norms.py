@@ -23,12 +23,16 @@ class RMSNorm(Norm):
     eps:     added to the mean square
     weight:  "plain" (scale = w), "centred" (scale = 1 + w, the sum taken in float32
              at load) or "none" (no tensor in the checkpoint)
+    groups:  the axis is cut into this many equal consecutive runs and each run is divided by
+             its own root mean square (1: the ordinary norm); a grouped norm needs a weight
     """
 
-    def __init__(self, size: int, eps: float, weight: str = "plain") -> None:
+    def __init__(self, size: int, eps: float, weight: str = "plain", groups: int = 1) -> None:
         if weight not in ("plain", "centred", "none"):
             raise ValueError(f"rms_norm weight convention {weight!r}")
-        self.size, self.eps, self.convention = size, float(eps), weight
+        if groups < 1 or size % groups or (groups > 1 and weight == "none"):
+            raise ValueError(f"rms_norm of {size} in {groups} groups (weight {weight!r})")
+        self.size, self.eps, self.convention, self.groups = size, float(eps), weight, groups
         self.weight = None
 
     def tensors(self) -> dict[str, TensorSpec]:
@@ -41,4 +45,6 @@ class RMSNorm(Norm):
             self.weight = (w + 1.0).contiguous() if self.convention == "centred" else w.contiguous()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.groups > 1:
+            return ops.streams_enter(x, None, 1, self.weight, self.eps, self.groups, self.runtime.dtype)
         return ops.rmsnorm(x, self.weight, self.eps, self.runtime.dtype)

@@ -21,13 +21,19 @@ _TABLES: dict[tuple[int, float, str], torch.Tensor] = {}
 
 @register_position("rotary")
 class Rotary(Position):
-    """Half-split rotary embedding over the first `dims` dims of each head.
+    """Rotary embedding over the first `dims` dims of each head.
 
-    theta: the base; inverse frequency i is theta^(-2i/dims), computed in float64 and
-           rounded once to float32, so every consumer multiplies the same constants.
+    theta:   the base; inverse frequency i is theta^(-2i/dims), computed in float64 and
+             rounded once to float32, so every consumer multiplies the same constants.
+    pairing: which dims turn together: "half" pairs dim i with i + dims/2, "interleaved" pairs
+             2i with 2i + 1. The table is the same; the mixer's kernel does the pairing, and a
+             mixer says which one it implements.
     """
 
-    def __init__(self, dims: int, theta: float) -> None:
+    def __init__(self, dims: int, theta: float, pairing: str = "half") -> None:
+        if pairing not in ("half", "interleaved"):
+            raise ValueError(f"rotary pairing {pairing!r}")
+        self.pairing = pairing
         if dims % 2 or dims <= 0:
             raise ValueError(f"rotary dims must be even and positive, got {dims}")
         if theta <= 0:

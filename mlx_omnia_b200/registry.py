@@ -47,6 +47,10 @@ class Architecture:
     tokenizer: Callable[[Path], Any] = read_tokenizer
     # The longest context the checkpoint declares (None: it declares none).
     max_context: Callable[[Any], int | None] = lambda config: None
+    # Sizes that no key of config.json gives and only the checkpoint's tensors do: called with the
+    # parsed configuration and `shape_of(file's tensor name) -> shape or None`, returns the
+    # configuration completed (None: the architecture needs no such thing).
+    sizes_from_tensors: Callable[[Any, Callable[[str], tuple[int, ...] | None]], Any] | None = None
     generation_defaults: Callable[[Path, Any], GenerationDefaults] | None = None
 
     def defaults(self, folder: Path, config: Any) -> GenerationDefaults:
@@ -71,12 +75,13 @@ def known_architectures() -> list[str]:
 
 
 def resolve_architecture(config: dict[str, Any]) -> Architecture:
-    """The architecture a config.json names; `architectures[0]` first, then `model_type`."""
-    import mlx_omnia_b200.architectures  # noqa: F401  (registers the built-in family)
+    """The architecture a config.json names; `architectures[0]` first, then `model_type`, then a
+    single `architecture` string."""
+    import mlx_omnia_b200.architectures  # noqa: F401  (registers the built-in families)
 
     names = list(config.get("architectures") or [])
-    for key in [*names[:1], config.get("model_type")]:
-        if key in _ARCHITECTURES:
+    for key in [*names[:1], config.get("model_type"), config.get("architecture")]:
+        if isinstance(key, str) and key in _ARCHITECTURES:
             return _ARCHITECTURES[key]
-    raise ValueError(f"unsupported architecture: architectures={names!r}, model_type={config.get('model_type')!r}; "
-                     f"known: {known_architectures()}")
+    raise ValueError(f"unsupported architecture: architectures={names!r}, model_type={config.get('model_type')!r}, "
+                     f"architecture={config.get('architecture')!r}; known: {known_architectures()}")

@@ -97,15 +97,22 @@ class DictSource:
         return self.tensors[name]
 
 
+def open_source(source):
+    """`source` as something with `names()`, `shape(name)` and `tensor(name)`: a model folder (a path)
+    and a dict of tensors under the checkpoint's names are wrapped, anything else is taken as it is."""
+    if isinstance(source, (str, Path)):
+        return FolderSource(source)
+    if isinstance(source, dict):
+        return DictSource(source)
+    return source
+
+
 def load_tensors(source, architecture: Architecture, config, expected: dict[str, TensorSpec],
                  runtime: Runtime) -> dict[str, torch.Tensor]:
     """Check and place on the device every tensor in `expected`. `source` is a model folder
     (a path), a dict of tensors under the checkpoint's names, or anything with `names()`,
     `shape(name)` and `tensor(name)`; whichever it is, the same check runs."""
-    if isinstance(source, (str, Path)):
-        source = FolderSource(source)
-    elif isinstance(source, dict):
-        source = DictSource(source)
+    source = open_source(source)
     dropped = set(architecture.dropped_tensors(config))
     found: dict[str, str] = {}
     unexpected: list[str] = []
