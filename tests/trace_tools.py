@@ -53,14 +53,16 @@ class Trace:
     def text(self) -> str:
         return "".join(json.dumps(s) + "\n" for s in self.steps)
 
-    def run(self, model: Path, dtype: str, out: Path, max_tokens: int | None = None, extra: list[str] = ()) -> dict:
+    def run(self, model: Path, dtype: str, out: Path, max_tokens: int | None = None, extra: list[str] = (),
+            vocab: int | None = None) -> dict:
         """Replay through bin/trace_run; returns {request: {position: logits}}."""
         command = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model), "--dtype", dtype,
                    "--out", str(out), "--max-tokens", str(max_tokens or self.peak), *extra]
         done = subprocess.run(command, input=self.text(), capture_output=True, text=True, timeout=600)
         assert done.returncode == 0, done.stderr[-4000:]
         assert done.stdout.split() == [w for s in self.steps for w in ("done", str(s["step"]))], done.stdout[-2000:]
-        vocab = json.loads((model / "config.json").read_text())["text_config"]["vocab_size"]
+        if vocab is None:
+            vocab = json.loads((model / "config.json").read_text())["text_config"]["vocab_size"]
         return self.gather(out, vocab)
 
     def run_engine(self, engine, out: Path, before_step=None) -> dict:
