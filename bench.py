@@ -17,6 +17,11 @@ time to read a prompt of 8,192 tokens in portions of 512 (a token budget).
 L2 holds, replayed from a CUDA graph) against the measured peaks: the streamed product
 of a decode step, the head, decode attention (GB/s), the prefill product and prefill
 attention (TFLOP/s). Data is synthetic: seeded uniform-random token ids.
+
+`--only fokalorn` is a record of its own: prefill and decode throughput of the Fokalorn design at a
+few sizes that resemble a real model's layers (random weights), beside Muse-Glimmer at equal width,
+depth, heads and feed-forward, and each kernel of the new design alone against its roofline beside
+the like kernel of Muse-Glimmer (`--size` picks one size).
 """
 
 from __future__ import annotations
@@ -541,6 +546,235 @@ def run(args) -> dict:
     }
 
 
+FOKALORN_SIZES = {
+    # width, feed-forward, heads (of 128), layers, latent rank, rotated dims, streams, norm groups
+    "1024": dict(width=1024, ff=3072, heads=8, layers=8, rank=256, rot=64, streams=2, groups=4),
+    "2048": dict(width=2048, ff=6144, heads=16, layers=8, rank=512, rot=64, streams=4, groups=8),
+    "4096": dict(width=4096, ff=12288, heads=32, layers=4, rank=512, rot=64, streams=4, groups=8),
+}
+FOKALORN_VOCAB = 32768
+
+
+def fokalorn_config(size: dict) -> dict:
+    """Three recurrent layers to one of latent attention, every layer with a feed-forward."""
+    delta = {"type": "channel_delta", "mlp": {"ff": size["ff"], "kind": "dense"},
+             "mixer": {"heads": size["heads"], "kv_heads": size["heads"], "dim": 128, "vdim": 128, "conv": 4,
+                       "decay_rank": 64, "gate_rank": 64}}
+    latent = {"type": "latent_attention", "mlp": {"ff": size["ff"], "kind": "dense"},
+              "mixer": {"heads": size["heads"], "dim": 128, "rot_dim": size["rot"], "vdim": 128, "kv_rank": size["rank"],
+                        "scale": (128 + size["rot"]) ** -0.5, "rot": {"base": 10000.0, "dims": size["rot"]}}}
+    layers = [json.loads(json.dumps(latent if i % 4 == 3 else delta)) for i in range(size["layers"])]
+    return {"architecture": "Fokalorn", "vocab": FOKALORN_VOCAB, "width": size["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5, "groups": size["groups"]}, "streams": size["streams"], "layers": layers}
+
+
+def muse_config_like(size: dict) -> dict:
+    raw = json.loads(json.dumps(CONFIG2))
+    n = size["layers"]
+    raw["text_config"].update(hidden_size=size["width"], intermediate_size=size["ff"], num_hidden_layers=n,
+                              num_attention_heads=size["heads"], num_key_value_heads=max(size["heads"] // 2, 1),
+                              vocab_size=FOKALORN_VOCAB, layer_types=["full_attention"] * n,
+                              layer_rope_theta=[1000000.0] * n, tie_word_embeddings=False)
+    return raw
+
+
+def run_fokalorn(args) -> dict:
+    """Prefill (one prompt of --prefill-tokens) and decode (--batch requests ending at --context tokens)
+    of Fokalorn and of Muse-Glimmer at equal sizes, then the new design's kernels alone."""
+    import torch
+
+    from mlx_omnia_b200.engine.engine import Engine, EngineArgs
+    from mlx_omnia_b200.engine.step import StepEntry
+    from mlx_omnia_b200.kernels import ops
+
+    measured, peak_source = peaks()
+    hbm, flops_peak = measured["hbm_gbs"] * 1e9, measured["bf16_tflops"] * 1e12
+    g = torch.Generator().manual_seed(SEED)
+    steps, warmup, batch, context, tokens = args.steps, max(args.warmup, 3), args.batch, args.context, args.prefill_tokens
+
+    def timed(fn, count, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(count):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / count
+
+    def whole_model(raw) -> dict:
+        engine = Engine.from_random(raw, SEED, EngineArgs(dtype="bfloat16", page_size=16, max_requests=batch + 1,
+                                                          cache_tokens=batch * (context + 16) + tokens + 16))
+        times = []
+        for index in range(warmup + 3):
+            request = engine.cache.open(f"p{index}")
+            ids = torch.randint(0, FOKALORN_VOCAB, (tokens,), generator=g).tolist()
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.runner.run([StepEntry(request, ids, [tokens - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            engine.cache.close(request.request_id)
+            times.append(start.elapsed_time(stop))
+        prefill_ms = statistics.median(times[warmup:])
+        requests = [engine.cache.open(f"d{i}") for i in range(batch)]
+        length = context - steps - warmup - 1
+        for r in requests:  # one prompt a step: a step of every prompt would need scratch for batch x length rows
+            engine.runner.run([StepEntry(r, torch.randint(0, FOKALORN_VOCAB, (length,), generator=g).tolist(), [])])
+        entries = lambda i: [StepEntry(r, [1 + i], [0]) for r in requests]
+        for i in range(warmup):
+            engine.runner.run(entries(i), copy=False)
+        torch.cuda.synchronize()
+        launches = ops.launches
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            engine.runner.run(entries(warmup + i), copy=False)
+        stop.record()
+        torch.cuda.synchronize()
+        decode_ms = start.elapsed_time(stop) / steps
+        ops.raise_on_error(engine.runtime.device)
+        weights = sum(t.numel() * t.element_size() for t in _model_tensors(engine.model))
+        out = {"prefill_tokens_per_s": round(tokens * 1000.0 / prefill_ms, 1), "prefill_ms": round(prefill_ms, 3),
+               "decode_tokens_per_s": round(batch * 1000.0 / decode_ms, 1), "decode_ms": round(decode_ms, 4),
+               "launches_per_decode_step": (ops.launches - launches) // steps, "weight_gb": round(weights / 1e9, 3)}
+        for r in requests:
+            engine.cache.close(r.request_id)
+        del engine
+        torch.cuda.empty_cache()
+        return out
+
+    def _model_tensors(model):
+        seen, out, stack = set(), [], [model]
+        while stack:
+            item = stack.pop()
+            if isinstance(item, torch.Tensor):
+                if item.is_cuda and item.data_ptr() not in seen:
+                    seen.add(item.data_ptr())
+                    out.append(item)
+            elif isinstance(item, (list, tuple)):
+                stack.extend(item)
+            elif isinstance(item, dict):
+                stack.extend(item.values())
+            elif hasattr(item, "__dict__") and type(item).__module__.startswith("mlx_omnia_b200.parts"):
+                stack.extend(v for k, v in vars(item).items() if k != "runtime")
+        return out
+
+    def kernels(size: dict) -> dict:
+        """Each kernel of the new design alone, at this size, with the bytes or FLOPs it cannot avoid;
+        and Muse-Glimmer's like kernels at the same heads. Times are per launch over `reps` launches
+        on operands larger than L2 where the operands are large at all."""
+        from mlx_omnia_b200.parts.base import KVSpec, KVView
+
+        dev, bf = torch.device("cuda:0"), torch.bfloat16
+        H, D, rank, rot, S = size["heads"], size["width"], size["rank"], size["rot"], size["streams"]
+        dk = dv = 128
+        out = {}
+
+        class Step:
+            pass
+
+        def step_of(lens, starts):
+            st = Step()
+            st.num_seqs, st.q_lens = len(lens), list(lens)
+            cu = [0]
+            for n in lens:
+                cu.append(cu[-1] + n)
+            st.cu_seqlens = torch.tensor(cu, dtype=torch.int32, device=dev)
+            st.state_slots = torch.arange(len(lens), dtype=torch.int32, device=dev)
+            st.positions = torch.tensor([s + i for s, n in zip(starts, lens) for i in range(n)], dtype=torch.int32, device=dev)
+            st.seq_lens = torch.tensor([s + n for s, n in zip(starts, lens)], dtype=torch.int32, device=dev)
+            st.seq_lens_host, st.max_q_len, st.max_seq_len = [s + n for s, n in zip(starts, lens)], max(lens), max(s + n for s, n in zip(starts, lens))
+            st.decode_only, st.workspace = all(n == 1 for n in lens), None
+            return st
+
+        def note(name, ms, bytes_=None, flops=None, like=None):
+            entry = {"us": round(ms * 1000.0, 2)}
+            if bytes_ is not None:
+                entry.update(gb_s=round(bytes_ / ms / 1e6, 1), frac_hbm=round(bytes_ / (ms / 1e3) / hbm, 4))
+            if flops is not None:
+                entry.update(tflops=round(flops / ms / 1e9, 2), frac_tensor=round(flops / (ms / 1e3) / flops_peak, 4))
+            out[name] = entry
+
+        for mode, lens, starts in (("prefill", [tokens], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+            st = step_of(lens, starts)
+            T = sum(lens)
+            # the recurrent mixer's kernels
+            C = 2 * H * dk + H * dv
+            proj = torch.randn(T, C + H, device=dev).to(bf)
+            taps = torch.randn(C, 4, device=dev)
+            conv_state = torch.zeros(len(lens) + 1, 3, C, device=dev)
+            S_state = torch.zeros(len(lens) + 1, H, dk, dv, device=dev)
+            a, gate = torch.randn(T, H * dk, device=dev).to(bf), torch.randn(T, H * dv, device=dev).to(bf)
+            A_log, dt_bias, nw = torch.zeros(H, device=dev), torch.zeros(H * dk, device=dev), torch.ones(dv, device=dev)
+            conv = ops.short_conv(proj, 0, C, taps, conv_state, st, 2 * H * dk, dk, 1e-6, H * dk, dk ** -0.5)
+            ms = timed(lambda: ops.short_conv(proj, 0, C, taps, conv_state, st, 2 * H * dk, dk, 1e-6, H * dk, dk ** -0.5), 20)
+            note(f"short_conv_{mode}", ms, bytes_=T * C * (2 + 4))
+            ms = timed(lambda: ops.delta_rule(conv, H, H, dk, dv, proj, 0, C, a, gate, A_log, dt_bias, nw, 1e-5, S_state,
+                                              conv_state, 4, st), 20)
+            state_bytes = 2 * len(lens) * H * dk * dv * 4
+            note(f"delta_rule_{mode}", ms, bytes_=state_bytes + T * (C * 4 + 2 * H * (dk + dv) * 2),
+                 flops=T * H * dk * dv * 2 * 3)
+            # latent attention's kernels
+            page, width = 16, rank + rot
+            pages = -(-st.max_seq_len // page)
+            cache = (torch.randn(len(lens) * pages, 1, 1, page, width, device=dev) * 0.3).to(bf)
+            table = torch.arange(len(lens) * pages, dtype=torch.int32, device=dev).view(len(lens), pages)
+            slots = torch.cat([table[i].long()[(st.positions[st.cu_seqlens[i]: st.cu_seqlens[i + 1]] // page).long()] * page
+                               + st.positions[st.cu_seqlens[i]: st.cu_seqlens[i + 1]].long() % page for i in range(len(lens))])
+            kv = KVView(cache, table, slots, page, None, True, KVSpec(((1, width),)))
+            qd = 128 + rot
+            lproj = (torch.randn(T, H * qd + width + H, device=dev) * 0.3).to(bf)
+            inv = torch.tensor([10000.0 ** (-2.0 * i / rot) for i in range(rot // 2)], device=dev)
+            dn_w = torch.ones(rank, device=dev)
+            ms = timed(lambda: ops.latent_prepare(lproj, 0, H, qd, H * qd, rank, rot, dn_w, 1e-5, inv, st.positions, kv), 20)
+            note(f"latent_prepare_{mode}", ms, bytes_=T * (2 * width + 2 * H * rot) * 2)
+            q_lat = (torch.randn(H, T, rank, device=dev) * 0.1).to(bf)
+            o_lat = torch.empty(H, T, rank, dtype=bf, device=dev)
+            q_rot = lproj[:, : H * qd].view(T, H, qd)[:, :, 128:]
+            sink = torch.zeros(H, device=dev)
+            reps = 3 if mode == "prefill" else 10
+            ms = timed(lambda: ops.latent_attention(q_lat, q_rot, kv, st, 0.07, sink, lproj[:, H * qd + width:], o_lat), reps, 1)
+            pairs = sum(s * n + n * (n + 1) // 2 for s, n in zip(starts, lens))
+            note(f"latent_attention_{mode}", ms, bytes_=sum(s + n for s, n in zip(starts, lens)) * width * 2 + 4 * T * H * rank,
+                 flops=2 * pairs * H * (width + rank))
+            # the residual streams' kernels, and the residual step of a single stream beside them
+            xs = torch.randn(T, S * D, device=dev)
+            y = torch.randn(T, D, device=dev).to(bf)
+            coef, mix, outc, w = torch.ones(S, device=dev), torch.eye(S, device=dev), torch.ones(S, device=dev), torch.ones(D, device=dev)
+            ms = timed(lambda: ops.streams_enter(xs, coef, S, w, 1e-5, size["groups"], bf), 20)
+            note(f"streams_enter_{mode}", ms, bytes_=T * (S * D * 4 + D * 2))
+            ms = timed(lambda: ops.streams_leave(xs, y, mix, outc, S), 20)
+            note(f"streams_leave_{mode}", ms, bytes_=T * (2 * S * D * 4 + D * 2))
+            x1 = torch.randn(T, D, device=dev)
+            ms = timed(lambda: ops.add_rmsnorm(x1, y, None, None, w, 1e-5), 20)
+            note(f"like:add_rmsnorm_{mode}", ms, bytes_=T * (2 * D * 4 + 2 * D * 2))
+            # Muse-Glimmer's attention at the same heads (half as many key/value heads, head size 128)
+            nkv = max(H // 2, 1)
+            gcache = (torch.randn(len(lens) * pages, 2, nkv, page, 128, device=dev) * 0.3).to(bf)
+            gkv = KVView(gcache, table, slots, page, None, True, KVSpec.keys_and_values(nkv, 128))
+            q = (torch.randn(T, H, 128, device=dev) * 0.3).to(bf)
+            ms = timed(lambda: ops.paged_attention(q, gkv, st, 0.09), 10, 2)
+            note(f"like:paged_attention_{mode}", ms, bytes_=sum(s + n for s, n in zip(starts, lens)) * 2 * nkv * 128 * 2 + 4 * T * H * 128,
+                 flops=2 * pairs * H * 256)
+        ops.raise_on_error(dev)
+        return out
+
+    record = {"metric": "Fokalorn beside Muse-Glimmer at equal sizes", "unit": "tokens/s", "dtype": "bf16",
+              "data": "synthetic: seeded uniform-random token ids, random weights",
+              "config": {"prefill_tokens": tokens, "decode_batch": batch, "decode_context": context, "vocab": FOKALORN_VOCAB,
+                         "peaks": peak_source}, "sizes": {}}
+    for name in ([args.size] if args.size else list(FOKALORN_SIZES)):
+        size = FOKALORN_SIZES[name]
+        record["sizes"][name] = {"fokalorn": whole_model(fokalorn_config(size)),
+                                 "muse_glimmer": whole_model(muse_config_like(size)),
+                                 "kernels": kernels(size), "layers": size["layers"]}
+    return record
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -552,7 +786,7 @@ def main() -> int:
     parser.add_argument("--timeline", action="store_true",
                         help="with --only decode|prefill and OMNIA_TIMELINE=1 in the environment: one step's "
                              "kernels with the time each takes in the stream, on stderr")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "portions", "sampling", "products", "elementwise"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "portions", "sampling", "products", "elementwise", "fokalorn"], default="all",
                         help="time one part only (small cases for profilers); prints a short record")
     parser.add_argument("--config", type=int, choices=sorted(CONFIGS), default=2,
                         help="with --only: the sizes of another benchmark configuration (3: 36 layers, hidden 4096, "
@@ -563,6 +797,8 @@ def main() -> int:
     parser.add_argument("--pool-tokens", type=int, default=0, help="at least this many tokens of cache pool (default: what the run needs)")
     parser.add_argument("--portion", type=int, default=256,
                         help="--only mixed: tokens of a prompt that run beside --batch decoding requests")
+    parser.add_argument("--size", choices=sorted(FOKALORN_SIZES), default=None,
+                        help="--only fokalorn: one size instead of all")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -576,6 +812,9 @@ def main() -> int:
         print("bench.py: the full record is of configuration 2; give --only decode|prefill|mixed with --config")
         return 2
     args.context = args.context or CONFIGS[args.config][1]
+    if args.only == "fokalorn":
+        print(json.dumps(run_fokalorn(args)))
+        return 0
     if args.only == "all":
         args.warmup = max(args.warmup, 3)
     print(json.dumps(run(args)))
