@@ -1073,16 +1073,65 @@ def latent_prepare(proj: torch.Tensor, q_col: int, heads: int, q_dim: int, down_
               _stream()), "latent_prepare")
 
 
+def latent_tc_supported(q_lat: torch.Tensor, q_rot: torch.Tensor, out: torch.Tensor, scale: float) -> bool:
+    """The tensor-core kernel takes bfloat16, a latent that is a multiple of 64 wide, a row (latent
+    and rotated part) that is a multiple of 32, a positive scale, and operands whose rows start on
+    16 bytes."""
+    rank, rot = q_lat.shape[2], q_rot.shape[2]
+    return (q_lat.dtype == torch.bfloat16 and rank % 64 == 0 and (rank + rot) % 32 == 0 and scale > 0
+            and all(t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0
+                    for t in (q_lat, q_rot, out)))
+
+
+def latent_split_plan(q_lens, heads: int, longest: int, rows_per_block: int, sms: int) -> tuple[int, int]:
+    """(splits, keys per split) of the tensor-core latent attention kernel: one split while the step's
+    row blocks fill the GPU; otherwise the keys are cut (in multiples of 32, at least 128 a split) so
+    that about two blocks run on every SM."""
+    blocks = sum(-(-q * heads // rows_per_block) for q in q_lens)
+    if blocks >= sms or longest <= 128:
+        return 1, 0
+    splits = min(-(-2 * sms // blocks), -(-longest // 128))
+    chunk = -(-(-(-longest // splits)) // 32) * 32
+    return -(-longest // chunk), chunk
+
+
 def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, kv: KVView, step: StepContext, scale: float,
-                     sink: torch.Tensor | None, gate: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:
+                     sink: torch.Tensor | None, gate: torch.Tensor | None, out: torch.Tensor,
+                     tensor_cores: bool | None = None) -> torch.Tensor:
     """Causal attention of every head over the cache's latent rows (see csrc/attention_latent.cu).
     q_lat [heads, tokens, rank], q_rot [tokens, heads, rot] and out [heads, tokens, rank] may be
     strided views (last dim contiguous); gate [tokens, >= heads] holds one logit per head in its
-    first columns; sink float32 [heads]."""
+    first columns; sink float32 [heads]. bfloat16 of supported widths runs on the tensor-core kernel
+    (csrc/attention_latent_tc.cu; `tensor_cores` False keeps it off), everything else, the 32-bit
+    path among it, on the generic one."""
     heads, tokens, rank = q_lat.shape
     rot = q_rot.shape[2]
     if q_lat.stride(2) != 1 or q_rot.stride(2) != 1 or out.stride(2) != 1 or (gate is not None and gate.stride(1) != 1):
         raise KernelError("latent_attention wants the last dim of its operands contiguous")
+    if tensor_cores is not False and latent_tc_supported(q_lat, q_rot, out, scale):
+        most_rows = step.max_q_len * heads
+        groups = 4 if most_rows > 32 else 2 if most_rows > 16 else 1
+        defines = {"LATENT_RANK": rank, "LATENT_ROT": rot, "LATENT_ROW_GROUPS": groups}
+        # The bound on a request's length that is fixed for a captured step: its block table's width.
+        longest = kv.block_table.shape[1] * kv.page_size
+        splits, chunk = latent_split_plan(step.q_lens, heads, longest, 16 * groups, sm_count(q_lat.device))
+        part_o = part_ml = None
+        if splits > 1:
+            part_o, part_ml = _step_buffers(step, q_lat.device, {
+                "latent_part_o": (tokens * heads * splits * rank, torch.float32, False),
+                "latent_part_ml": (tokens * heads * splits * 2, torch.float32, False)})
+        fn = _function("attention_latent_tc", "omnia_latent_attention_tc",
+                       [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p,
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                        c_void_p], defines)
+        _check(fn(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(1), q_rot.stride(0),
+                  _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens), _ptr(sink),
+                  _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out), out.stride(0), out.stride(1),
+                  _ptr(part_o), _ptr(part_ml), tokens, step.num_seqs, step.max_q_len, kv.block_table.shape[1],
+                  kv.pages.shape[0], heads, kv.page_size, kv.window or 0, splits, chunk, scale,
+                  _ptr(error_word(q_lat.device)), _stream()), "latent_attention_tc")
+        return out
     if rank > LATENT_MAX_RANK:
         raise KernelError(f"latent_attention takes a latent of at most {LATENT_MAX_RANK}, got {rank}")
     fn = _function("attention_latent", "omnia_latent_attention",

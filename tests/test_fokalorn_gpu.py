@@ -49,6 +49,7 @@ class Batch:
         self.state_slots = torch.tensor(slots or list(range(len(lens))), dtype=torch.int32, device=CUDA)
         self.positions = torch.tensor([s + i for s, n in zip(starts, lens) for i in range(n)], dtype=torch.int32, device=CUDA)
         self.seq_lens = torch.tensor([s + n for s, n in zip(starts, lens)], dtype=torch.int32, device=CUDA)
+        self.max_q_len, self.max_seq_len, self.workspace = max(lens), max(s + n for s, n in zip(starts, lens)), None
 
 
 # ---- each mechanism alone -------------------------------------------------------------------
@@ -160,7 +161,8 @@ def test_short_convolution_and_delta_rule(H, G, dk, dv, K):
     assert float((S[[1, 3]] - 3.0).abs().max()) == 0.0
 
 
-def latent_case(H, dn, dr, dims, rank, page, lens, window=None, sink=True, seed=0, dtype=torch.float32, boost=None):
+def latent_case(H, dn, dr, dims, rank, page, lens, window=None, sink=True, seed=0, dtype=torch.float32, boost=None,
+                tensor_cores=None, first=None):
     """Latent attention's two kernels over requests of `lens` tokens, each read in two portions into
     scattered pages, against the plain implementation's expanded form (identity expansions, so that
     its keys and values are the latent rows themselves)."""
@@ -202,12 +204,14 @@ def latent_case(H, dn, dr, dims, rank, page, lens, window=None, sink=True, seed=
         expect.append(torch.einsum("hts,sr->thr", weights, c) * torch.sigmoid(gates[s].to(F64))[:, :, None])
     got = [[] for _ in lens]
     for part in (0, 1):
-        cuts = [(0, max(n // 2, 1)) if part == 0 else (max(n // 2, 1), n) for n in lens]
+        at = [min(max(first or n // 2, 1), n) for n in lens]
+        cuts = [(0, c) if part == 0 else (c, n) for c, n in zip(at, lens)]
         live = [s for s, (lo, hi) in enumerate(cuts) if hi > lo]
         step = Batch([cuts[s][1] - cuts[s][0] for s in live], [cuts[s][0] for s in live])
         take = lambda store: torch.cat([store[s][cuts[s][0]: cuts[s][1]] for s in live])
         tokens = int(step.positions.shape[0])
-        proj = torch.cat([take(qs).reshape(tokens, H * qd), take(downs), take(gates)], dim=1).to(dtype).to(CUDA).contiguous()
+        proj = torch.cat([take(qs).reshape(tokens, H * qd), take(downs), take(gates)], dim=1)
+        proj = torch.nn.functional.pad(proj, (0, -proj.shape[1] % 8)).to(dtype).to(CUDA).contiguous()
         slot = torch.cat([table[s].long()[torch.arange(*cuts[s]) // page].cpu() * page + torch.arange(*cuts[s]) % page
                           for s in live]).to(CUDA)
         kv = KVView(cache, table[live].contiguous(), slot, page, window, True, KVSpec(((1, width),), window))
@@ -215,7 +219,10 @@ def latent_case(H, dn, dr, dims, rank, page, lens, window=None, sink=True, seed=
         q3 = proj[:, : H * qd].view(tokens, H, qd)
         q_lat = take(q_lats).to(dtype).to(CUDA).transpose(0, 1).contiguous()
         out = torch.empty(H, tokens, rank, dtype=dtype, device=CUDA)
-        ops.latent_attention(q_lat, q3[:, :, dn:], kv, step, 0.3, sinks.to(CUDA) if sink else None, proj[:, H * qd + width:], out)
+        if tensor_cores:
+            assert ops.latent_tc_supported(q_lat, q3[:, :, dn:], out, 0.3)
+        ops.latent_attention(q_lat, q3[:, :, dn:], kv, step, 0.3, sinks.to(CUDA) if sink else None, proj[:, H * qd + width:], out,
+                             tensor_cores=tensor_cores)
         lo = 0
         for s in live:
             n = cuts[s][1] - cuts[s][0]
@@ -246,6 +253,34 @@ def test_latent_attention_finds_a_far_key_and_counts_the_sink():
     assert rel(got16[0], expect16[0]) < 3e-2
 
 
+@pytest.mark.parametrize("H,dn,dr,dims,rank,page,window,sink", [
+    (3, 24, 32, 8, 64, 16, None, True), (16, 64, 64, 64, 128, 16, None, True), (20, 32, 64, 32, 192, 4, 21, False),
+    (1, 16, 32, 32, 64, 8, None, True), (5, 8, 64, 64, 512, 16, 40, True)])
+def test_latent_attention_on_the_tensor_cores(H, dn, dr, dims, rank, page, window, sink):
+    """The bfloat16 kernel against the plain implementation and against the generic kernel, with
+    lengths around page and tile borders; blocks of 16, 32 and 64 rows come from the head counts."""
+    lens = [1, 31, 32, 33, 65, 100]
+    got, expect = latent_case(H, dn, dr, dims, rank, page, lens, window, sink, seed=H, dtype=torch.bfloat16, tensor_cores=True)
+    plain_kernel, _ = latent_case(H, dn, dr, dims, rank, page, lens, window, sink, seed=H, dtype=torch.bfloat16, tensor_cores=False)
+    for a, b, c in zip(got, expect, plain_kernel):
+        assert rel(a, b) < 3e-2
+        assert rel(a, c) < 2e-2
+
+
+def test_latent_attention_on_the_tensor_cores_with_the_keys_cut():
+    """Few rows over many keys: the key range is cut into chunks that are merged afterwards (a long
+    prompt's last portion, then its last token alone), a far key among them; the sink counts once."""
+    for first in (1100, 1199):
+        got, expect = latent_case(4, 32, 32, 32, 64, 16, [1200, 37], seed=3, dtype=torch.bfloat16, tensor_cores=True,
+                                  boost=(0, 1199, 70), first=first)
+        assert ops.latent_split_plan([1200 - first], 4, 1200, 64, ops.sm_count(CUDA))[0] > 1
+        for a, b in zip(got, expect):
+            assert rel(a, b) < 3e-2
+        without, _ = latent_case(4, 32, 32, 32, 64, 16, [1200, 37], seed=3, dtype=torch.bfloat16, tensor_cores=True,
+                                 boost=(0, 1199, 70), first=first, sink=False)
+        assert rel(without[0], expect[0]) > 3e-2
+
+
 # ---- the engine ------------------------------------------------------------------------------
 
 
@@ -258,6 +293,26 @@ def engine_for(name, dtype="float32", page=4, tokens=1024, requests=4, graphs=Tr
 
 
 TOLERANCE = {"float32": 3e-4, "bfloat16": 6e-2}
+
+
+def test_engine_with_tensor_core_latent_attention(tmp_path):
+    """Sizes at which bfloat16 latent attention runs on the tensor cores: whole, in portions, decoded
+    from captured steps, two requests side by side, against the plain implementation."""
+    raw = fc.config("Y")
+    raw["width"] = 128
+    raw["layers"][1]["mixer"].update(heads=6, dim=32, rot_dim=32, kv_rank=64, vdim=24, rot={"base": 1000.0, "dims": 32})
+    raw["layers"].append(fc.config("X")["layers"][1])
+    raw, weights, engine = engine_for("Y", "bfloat16", page=16, tokens=1024, raw=raw)
+    ids = {"a": fc.prompt(150, raw["vocab"], 1), "b": fc.prompt(61, raw["vocab"], 2)}
+    trace = Trace()
+    trace.step({"a": ids["a"][:97]})
+    trace.step({"a": ids["a"][97:130], "b": ids["b"][:60]})
+    for t in range(130, 150):
+        trace.step({"a": ids["a"][t: t + 1], **({"b": ids["b"][60:]} if t == 130 else {})}, end=["b"] if t == 130 else [])
+    got = trace.run_engine(engine, tmp_path / "out", before_step=lambda e, record: poison_free_pages(e))
+    for r in ids:
+        positions, logits = stacked(got[r])
+        assert rel(logits, plain.forward(raw, weights, ids[r])) < TOLERANCE["bfloat16"], r
 
 
 @pytest.mark.parametrize("name", ["X", "Y", "Z"])
