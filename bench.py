@@ -710,13 +710,13 @@ def run_fokalorn(args) -> dict:
             S_state = torch.zeros(len(lens) + 1, H, dk, dv, device=dev)
             a, gate = torch.randn(T, H * dk, device=dev).to(bf), torch.randn(T, H * dv, device=dev).to(bf)
             A_log, dt_bias, nw = torch.zeros(H, device=dev), torch.zeros(H * dk, device=dev), torch.ones(dv, device=dev)
-            conv = ops.short_conv(proj, 0, C, taps, conv_state, st, 2 * H * dk, dk, 1e-6, H * dk, dk ** -0.5)
-            ms = timed(lambda: ops.short_conv(proj, 0, C, taps, conv_state, st, 2 * H * dk, dk, 1e-6, H * dk, dk ** -0.5), 20)
-            note(f"short_conv_{mode}", ms, bytes_=T * C * (2 + 4))
-            ms = timed(lambda: ops.delta_rule(conv, H, H, dk, dv, proj, 0, C, a, gate, A_log, dt_bias, nw, 1e-5, S_state,
-                                              conv_state, 4, st), 20)
+            run_conv = lambda: ops.short_conv(proj, 0, C, taps, conv_state, st, 2 * H * dk, dk, 1e-6, H * dk, dk ** -0.5,
+                                              a, A_log, dt_bias, C, H)
+            conv = run_conv()
+            note(f"short_conv_{mode}", timed(run_conv, 20), bytes_=T * (C * (2 + 4) + H * dk * (2 + 4)))
+            ms = timed(lambda: ops.delta_rule(conv, C, H, H, dk, dv, proj, 0, gate, nw, 1e-5, S_state, conv_state, 4, st), 20)
             state_bytes = 2 * len(lens) * H * dk * dv * 4
-            note(f"delta_rule_{mode}", ms, bytes_=state_bytes + T * (C * 4 + 2 * H * (dk + dv) * 2),
+            note(f"delta_rule_{mode}", ms, bytes_=state_bytes + T * ((C + H * dk) * 4 + 2 * H * dv * 2),
                  flops=T * H * dk * dv * 2 * 3)
             # latent attention's kernels
             page, width = 16, rank + rot

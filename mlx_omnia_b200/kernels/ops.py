@@ -1011,42 +1011,70 @@ MAX_CONV_TAPS = 16
 
 def short_conv(proj: torch.Tensor, col0: int, channels: int, taps: torch.Tensor, state: torch.Tensor,
                step: StepContext, unit_channels: int, unit_dim: int, unit_eps: float, scaled_channels: int,
-               scale: float) -> torch.Tensor:
-    """silu(causal depth-wise convolution) of columns [col0, col0 + channels) of the projected rows,
+               scale: float, a_rows: torch.Tensor | None = None, A_log: torch.Tensor | None = None,
+               dt_bias: torch.Tensor | None = None, beta_col: int = 0, beta_heads: int = 0) -> torch.Tensor:
+    """Everything of a recurrent mixer's token that needs no other token's result, one float32 row
+    [y | decay | beta] a token (rows a multiple of 4 floats apart):
+    y = silu(causal depth-wise convolution) of columns [col0, col0 + channels) of the projected rows,
     the inputs before a portion read from `state` [slots, taps - 1, channels]; the first
-    `unit_channels` outputs are made unit vectors in runs of `unit_dim`, the first `scaled_channels`
-    of those also multiplied by `scale`. -> float32 [tokens, channels]. The state is not moved on
-    here (`delta_rule` does that)."""
+    `unit_channels` of y are made unit vectors in runs of `unit_dim`, the first `scaled_channels` of
+    those also multiplied by `scale`; decay = exp(-exp(A_log[head]) softplus(a_rows + dt_bias)) per
+    column of `a_rows` (heads x unit_dim); beta = sigmoid of the `beta_heads` columns of the projected
+    rows from `beta_col`. The state is not moved on here (`delta_rule` does that)."""
     tokens = proj.shape[0]
-    y = torch.empty(tokens, channels, dtype=torch.float32, device=proj.device)
+    gates = a_rows.shape[1] if a_rows is not None else 0
+    width = -(-(channels + gates + beta_heads) // 4) * 4
+    y = torch.empty(tokens, width, dtype=torch.float32, device=proj.device)
     fn = _function("delta_rule", "omnia_short_conv",
                    [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                    c_float, c_int, c_float, c_void_p, c_int, c_int, c_void_p], {"DELTA_DK": unit_dim})
+                    c_float, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
+                    c_int, c_int, c_void_p], {"DELTA_DK": unit_dim})
     _check(fn(_ptr(proj), proj.shape[1], col0, channels, taps.shape[1], _ptr(taps), _ptr(state), _ptr(step.cu_seqlens),
               _ptr(step.state_slots), step.num_seqs, unit_channels, unit_dim, unit_eps, scaled_channels, scale,
-              _ptr(y), tokens, _code(proj.dtype), _stream()), "short_conv")
+              _ptr(a_rows), a_rows.stride(0) if a_rows is not None else 0, _ptr(A_log), _ptr(dt_bias), gates, beta_col,
+              beta_heads, _ptr(y), width, tokens, _code(proj.dtype), _stream()), "short_conv")
     return y
 
 
-def delta_rule(conv: torch.Tensor, groups: int, heads: int, dk: int, dv: int, proj: torch.Tensor, in_col: int,
-               beta_col: int, a_rows: torch.Tensor, gate_rows: torch.Tensor, A_log: torch.Tensor,
-               dt_bias: torch.Tensor, norm_weight: torch.Tensor, eps: float, S: torch.Tensor,
-               conv_state: torch.Tensor, taps: int, step: StepContext) -> torch.Tensor:
+def delta_parts(requests: int, heads: int, dv: int, sms: int) -> int:
+    """Into how many runs of columns the recurrence kernel cuts a head's value channels: 1 (the block
+    then also norms the head's output) when the step's (request, head) pairs give half the SMs a block
+    each; otherwise the fewest equal runs (of a multiple of 4 columns, at least 16) that give every SM
+    about two blocks."""
+    blocks = requests * heads
+    if 2 * blocks >= sms:
+        return 1
+    best = 1
+    for parts in range(1, dv + 1):
+        if dv % parts or (dv // parts) % 4 or dv // parts < 16:
+            continue
+        best = parts
+        if blocks * parts >= 2 * sms:
+            break
+    return best
+
+
+def delta_rule(conv: torch.Tensor, channels: int, groups: int, heads: int, dk: int, dv: int, proj: torch.Tensor,
+               in_col: int, gate_rows: torch.Tensor, norm_weight: torch.Tensor, eps: float, S: torch.Tensor,
+               conv_state: torch.Tensor, taps: int, step: StepContext, parts: int | None = None) -> torch.Tensor:
     """The gated delta rule with a decay per head and key channel over this step's tokens, request by
     request from the state in `S` [slots, heads, dk, dv] (float32, updated in place), followed by the
-    RMS norm of each head's output, its weight and the sigmoid gate. Also moves `conv_state` on by
+    RMS norm of each head's output, its weight and the sigmoid gate (`gate_rows` [tokens, heads * dv]
+    logits). `conv` is `short_conv`'s output (q | k | v | decay | beta). Also moves `conv_state` on by
     this step's raw convolution inputs (columns from `in_col` of `proj`). -> [tokens, heads * dv]"""
     tokens = proj.shape[0]
     out = torch.empty(tokens, heads * dv, dtype=proj.dtype, device=proj.device)
-    defines = {"DELTA_DK": dk}
+    if parts is None:
+        parts = delta_parts(step.num_seqs, heads, dv, sm_count(proj.device))
+    raw = torch.empty(tokens, heads * dv, dtype=torch.float32, device=proj.device) if parts > 1 else None
     fn = _function("delta_rule", "omnia_delta_rule",
-                   [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
-                    c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                    c_int, c_void_p, c_int, c_void_p], defines)
-    _check(fn(_ptr(conv), conv.shape[1], groups, heads, dv, _ptr(proj), proj.shape[1], in_col, beta_col,
-              _ptr(a_rows), a_rows.shape[1], _ptr(gate_rows), gate_rows.shape[1], _ptr(A_log), _ptr(dt_bias),
-              _ptr(norm_weight), eps, _ptr(S), _ptr(conv_state), taps, _ptr(step.cu_seqlens),
-              _ptr(step.state_slots), step.num_seqs, _ptr(out), _code(proj.dtype), _stream()), "delta_rule")
+                   [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
+                    c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                    c_int, c_void_p], {"DELTA_DK": dk})
+    _check(fn(_ptr(conv), conv.shape[1], channels, groups, heads, dv, parts, _ptr(proj), proj.shape[1], in_col,
+              _ptr(gate_rows), gate_rows.stride(0), _ptr(norm_weight), eps, _ptr(S), _ptr(conv_state), taps,
+              _ptr(step.cu_seqlens), _ptr(step.state_slots), step.num_seqs, tokens, _ptr(out), _ptr(raw),
+              _code(proj.dtype), _stream()), "delta_rule")
     return out
 
 

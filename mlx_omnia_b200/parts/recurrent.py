@@ -82,11 +82,10 @@ class ChannelDelta(Mixer):
         step, state = ctx.step, ctx.state
         proj = ops.linear(h, self.in_proj)
         qk = self.kv_heads * self.dim
-        conv = ops.short_conv(proj, 0, self.channels, self.taps, state["conv"], step, 2 * qk, self.dim, self.unit_eps,
-                              qk, self.dim ** -0.5)
         decay = ops.linear(proj[:, self.a1_col: self.a1_col + self.decay_rank], self.a2)
         gate = ops.linear(proj[:, self.g1_col: self.g1_col + self.gate_rank], self.g2)
-        out = ops.delta_rule(conv, self.kv_heads, self.heads, self.dim, self.vdim, proj, 0, self.beta_col, decay, gate,
-                             self.A_log, self.dt_bias, self.norm_weight, self.norm_eps, state["S"], state["conv"],
-                             self.conv, step)
+        conv = ops.short_conv(proj, 0, self.channels, self.taps, state["conv"], step, 2 * qk, self.dim, self.unit_eps,
+                              qk, self.dim ** -0.5, decay, self.A_log, self.dt_bias, self.beta_col, self.heads)
+        out = ops.delta_rule(conv, self.channels, self.kv_heads, self.heads, self.dim, self.vdim, proj, 0, gate,
+                             self.norm_weight, self.norm_eps, state["S"], state["conv"], self.conv, step)
         return ops.linear(out, self.o)

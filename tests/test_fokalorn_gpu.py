@@ -108,14 +108,15 @@ def test_activation(kind):
     assert rel(ops.activation(zb, kind), plain.ACTIVATIONS[kind](zb.cpu().double())) < 1e-2
 
 
-@pytest.mark.parametrize("H,G,dk,dv,K", [(4, 2, 24, 40, 4), (1, 1, 8, 8, 1), (3, 3, 12, 20, 5), (2, 1, 64, 128, 2),
-                                          (2, 2, 128, 64, 3), (1, 1, 32, 200, 2)])
-def test_short_convolution_and_delta_rule(H, G, dk, dv, K):
+@pytest.mark.parametrize("H,G,dk,dv,K,parts", [(4, 2, 24, 40, 4, 1), (1, 1, 8, 8, 1, None), (3, 3, 12, 20, 5, 5),
+                                                (2, 1, 64, 128, 2, None), (2, 2, 128, 64, 3, 4), (1, 1, 32, 200, 2, 2),
+                                                (2, 2, 128, 128, 4, 1), (4, 2, 24, 40, 4, 2)])
+def test_short_convolution_and_delta_rule(H, G, dk, dv, K, parts):
     """The recurrent mixer's two kernels over three requests cut into portions of 1 to 9 tokens, one
     request joining late into a slot that another has left, against the whole-sequence recurrence."""
     g = torch.Generator().manual_seed(H * 7 + dk)
     C = 2 * G * dk + H * dv
-    lens = {"a": 23, "b": 9, "c": 14}
+    lens = {"a": 60, "b": 9, "c": 14}
     raw = {r: torch.randn(n, C, generator=g) for r, n in lens.items()}
     beta_l = {r: torch.randn(n, H, generator=g) for r, n in lens.items()}
     a_l = {r: torch.randn(n, H * dk, generator=g) for r, n in lens.items()}
@@ -139,7 +140,8 @@ def test_short_convolution_and_delta_rule(H, G, dk, dv, K):
 
     S = torch.full((4, H, dk, dv), 3.0, device=CUDA)
     conv_state = torch.full((4, K - 1, C), 3.0, device=CUDA)
-    plan = [{"a": 9, "b": 2}, {"a": 1, "b": 7}, {"a": 3}, {"a": 2, "c": 5}, {"c": 1, "a": 8}, {"c": 8}]
+    lens = {"a": 60, "b": 9, "c": 14}
+    plan = [{"a": 9, "b": 2}, {"a": 1, "b": 7}, {"a": 3}, {"a": 2, "c": 5}, {"c": 1, "a": 8}, {"c": 8, "a": 37}]
     slots, at, got = {"a": 2, "b": 0, "c": 0}, {r: 0 for r in lens}, {r: [] for r in lens}
     for portions in plan:
         for r in portions:
@@ -149,9 +151,10 @@ def test_short_convolution_and_delta_rule(H, G, dk, dv, K):
         step = Batch(list(portions.values()), [at[r] for r in portions], [slots[r] for r in portions])
         cut = lambda store: torch.cat([store[r][at[r]: at[r] + n] for r, n in portions.items()])
         proj = torch.cat([cut(raw), cut(beta_l)], dim=1).to(CUDA).contiguous()
-        conv = ops.short_conv(proj, 0, C, taps.to(CUDA), conv_state, step, 2 * G * dk, dk, 1e-6, G * dk, dk ** -0.5)
-        out = ops.delta_rule(conv, G, H, dk, dv, proj, 0, C, cut(a_l).to(CUDA), cut(gate_l).to(CUDA), A_log.to(CUDA),
-                             dt_bias.to(CUDA), nw.to(CUDA), 1e-5, S, conv_state, K, step)
+        conv = ops.short_conv(proj, 0, C, taps.to(CUDA), conv_state, step, 2 * G * dk, dk, 1e-6, G * dk, dk ** -0.5,
+                              cut(a_l).to(CUDA), A_log.to(CUDA), dt_bias.to(CUDA), C, H)
+        out = ops.delta_rule(conv, C, G, H, dk, dv, proj, 0, cut(gate_l).to(CUDA), nw.to(CUDA), 1e-5, S, conv_state, K,
+                             step, parts=parts)
         lo = 0
         for r, n in portions.items():
             got[r].append(out[lo: lo + n])
