@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(THREADS) latent_attention_tc_kernel(const Args
     cp_async_commit();
     const bf16* kt = ks + stage * BN * ROW;
     // Scores of 16 rows against the 8 keys of this warp's quarter.
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    float s[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};  // two chains of products
 #pragma unroll 4
     for (int k2 = 0; k2 < KSTEPS / 2; ++k2) {
       unsigned qa[4], qb[4], b[4];
@@ -199,8 +199,10 @@ __global__ void __launch_bounds__(THREADS) latent_attention_tc_kernel(const Args
       ldmatrix_x4(qb, qs + (rg * 16 + (mat & 1) * 8 + (lane & 7)) * ROW + (2 * k2 + 1) * 16 + (mat >> 1) * 8);
       ldmatrix_x4(b, kt + (cw * 8 + (lane & 7)) * ROW + k2 * 32 + mat * 8);
       mma_bf16(s, qa, b[0], b[1]);
-      mma_bf16(s, qb, b[2], b[3]);
+      mma_bf16(s_odd, qb, b[2], b[3]);
     }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[e] += s_odd[e];
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -292,30 +294,49 @@ __global__ void __launch_bounds__(THREADS) latent_attention_tc_kernel(const Args
   }
 }
 
-// One block per (token, head): its chunks merged in ascending order.
+// A block per (token, head) and 128 latent columns: the row's chunks merged in ascending order,
+// their weights worked out once, the partial rows read side by side.
+#define LATENT_MAX_SPLITS 256
 __global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
                                     int heads, const float* __restrict__ sink, const bf16* __restrict__ gate,
                                     int gate_stride, bf16* __restrict__ out, long long out_stride_h,
                                     long long out_stride_t) {
   pdl_wait();
   pdl_launch_dependents();
+  __shared__ float weight[LATENT_MAX_SPLITS];
+  __shared__ float factor;
   const int row = blockIdx.x;
   const int token = row / heads, head = row % heads;
   const float* ml = part_ml + (size_t)row * splits * 2;
-  float top = -INFINITY;
-  for (int c = 0; c < splits; ++c) top = fmaxf(top, ml[2 * c]);
-  float total = 0.f;
-  for (int c = 0; c < splits; ++c) total += ml[2 * c] == -INFINITY ? 0.f : ml[2 * c + 1] * expf(ml[2 * c] - top);
-  const float f = finish_factor(top, total, sink, gate, gate_stride, token, head);
-  bf16* orow = out + head * out_stride_h + token * out_stride_t;
-  for (int i = threadIdx.x; i < RANK; i += blockDim.x) {
-    float acc = 0.f;
-    for (int c = 0; c < splits; ++c) {
+  if (threadIdx.x < 32) {
+    float top = -INFINITY;
+    for (int c = threadIdx.x; c < splits; c += 32) top = fmaxf(top, ml[2 * c]);
+    top = warp_max(top);
+    float total = 0.f;
+    for (int c = threadIdx.x; c < splits; c += 32) {
       const float w = ml[2 * c] == -INFINITY ? 0.f : expf(ml[2 * c] - top);
-      acc += w * part_o[((size_t)row * splits + c) * RANK + i];
+      weight[c] = w;
+      total += ml[2 * c + 1] * w;
     }
-    orow[i] = __float2bfloat16_rn(acc * f);
+    total = warp_sum(total);
+    if (threadIdx.x == 0) factor = finish_factor(top, total, sink, gate, gate_stride, token, head);
   }
+  __syncthreads();
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= RANK) return;
+  const float* po = part_o + (size_t)row * splits * RANK + i;
+  float acc = 0.f;
+  int c = 0;
+  for (; c + 4 <= splits; c += 4) {
+    const float x0 = po[(size_t)c * RANK], x1 = po[(size_t)(c + 1) * RANK], x2 = po[(size_t)(c + 2) * RANK],
+                x3 = po[(size_t)(c + 3) * RANK];
+    acc += weight[c] * x0;
+    acc += weight[c + 1] * x1;
+    acc += weight[c + 2] * x2;
+    acc += weight[c + 3] * x3;
+  }
+  for (; c < splits; ++c) acc += weight[c] * po[(size_t)c * RANK];
+  out[head * out_stride_h + token * out_stride_t + i] = __float2bfloat16_rn(acc * factor);
 }
 
 }  // namespace
@@ -331,7 +352,7 @@ extern "C" int omnia_latent_attention_tc(const void* q_lat, long long q_lat_stri
                                          int num_pages, int heads, int page_size, int window, int splits, int chunk,
                                          float scale, int* err, cudaStream_t stream) {
   if (tokens == 0 || num_seqs == 0) return 0;
-  if (heads < 1 || splits < 1 || (splits > 1 && (chunk < BN || chunk % BN != 0 || part_o == nullptr))) return (int)cudaErrorInvalidValue;
+  if (heads < 1 || splits < 1 || splits > LATENT_MAX_SPLITS || (splits > 1 && (chunk < BN || chunk % BN != 0 || part_o == nullptr))) return (int)cudaErrorInvalidValue;
   if ((q_lat_stride_h | q_lat_stride_t | q_rot_stride_h | q_rot_stride_t | out_stride_h | out_stride_t) % 8 != 0 ||
       ((reinterpret_cast<uintptr_t>(q_lat) | reinterpret_cast<uintptr_t>(q_rot) | reinterpret_cast<uintptr_t>(cache)) & 15) != 0 ||
       (reinterpret_cast<uintptr_t>(out) & 3) != 0)
@@ -356,7 +377,7 @@ extern "C" int omnia_latent_attention_tc(const void* q_lat, long long q_lat_stri
   launch_pdl(latent_attention_tc_kernel, grid, dim3(THREADS), smem, stream, a);
   int code = OMNIA_LAUNCH_RESULT();
   if (code != 0 || splits == 1) return code;
-  launch_pdl(latent_merge_kernel, dim3(tokens * heads), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
+  launch_pdl(latent_merge_kernel, dim3(tokens * heads, (RANK + 127) / 128), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml,
              splits, heads, sink, (const bf16*)gate, gate_stride, (bf16*)out, out_stride_h, out_stride_t);
   return OMNIA_LAUNCH_RESULT();
 }

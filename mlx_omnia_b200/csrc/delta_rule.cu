@@ -44,45 +44,61 @@ __global__ void short_conv_kernel(const T* __restrict__ proj, int stride, int co
                                   int scaled_channels, float scale, const T* __restrict__ a_rows, int a_stride,
                                   const float* __restrict__ A_log, const float* __restrict__ dt_bias,
                                   int gate_channels, int beta_col, int beta_heads, float* __restrict__ y,
-                                  int out_stride) {
+                                  int out_stride, int chunk) {
   pdl_wait();
   pdl_launch_dependents();
-  extern __shared__ float val[];  // [C]
+  extern __shared__ float val[];  // [chunk]: this block's channels
   const int t = blockIdx.x;
+  // Block y of a token takes channels [y chunk, (y + 1) chunk), chunk a multiple of unit_dim, so a
+  // unit-normed run never straddles two blocks; and its share of the decays and betas.
+  const int c_lo = blockIdx.y * chunk, c_hi = min(C, c_lo + chunk);
   const int seq = request_of(cu_seqlens, num_seqs, t);
   const int start = cu_seqlens[seq];
   const float* tail = state + (size_t)state_slots[seq] * (K - 1) * C;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < K; ++j) {
-      const int back = K - 1 - j;  // how many tokens before t
-      const int src = t - back;
-      float x;
-      if (src >= start) x = to_f32(proj[(size_t)src * stride + col0 + c]);
-      else x = tail[(size_t)(K - 1 - (start - src)) * C + c];
-      acc += taps[(size_t)c * K + j] * x;
-    }
-    val[c] = acc / (1.f + expf(-acc));
-  }
   float* row = y + (size_t)t * out_stride;
-  for (int i = threadIdx.x; i < gate_channels; i += blockDim.x) {
-    const float z = to_f32(a_rows[(size_t)t * a_stride + i]) + dt_bias[i];
-    const float softplus = z > 20.f ? z : log1pf(expf(z));
-    row[C + i] = expf(-expf(A_log[i / unit_dim]) * softplus);
+  const int extras = gate_channels + beta_heads;
+  const int per = (extras + gridDim.y - 1) / gridDim.y;
+  // The loads of the decays' logits are asked for first; they are used last.
+  const int e0 = blockIdx.y * per + threadIdx.x;
+  float z_first = 0.f;
+  if (threadIdx.x < per && e0 < gate_channels) z_first = to_f32(a_rows[(size_t)t * a_stride + e0]);
+  for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) {
+    float x[DELTA_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < DELTA_MAX_TAPS; ++j) {
+      if (j >= K) break;
+      const int src = t - (K - 1 - j);
+      x[j] = src >= start ? to_f32(proj[(size_t)src * stride + col0 + c])
+                          : tail[(size_t)(K - 1 - (start - src)) * C + c];
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < DELTA_MAX_TAPS; ++j) {
+      if (j >= K) break;
+      acc += taps[(size_t)c * K + j] * x[j];
+    }
+    val[c - c_lo] = acc / (1.f + expf(-acc));
   }
-  for (int h = threadIdx.x; h < beta_heads; h += blockDim.x)
-    row[C + gate_channels + h] = 1.f / (1.f + expf(-to_f32(proj[(size_t)t * stride + beta_col + h])));
+  for (int e = blockIdx.y * per + threadIdx.x; e < min(extras, (int)(blockIdx.y + 1) * per); e += blockDim.x) {
+    if (e < gate_channels) {
+      const float z = (e == e0 ? z_first : to_f32(a_rows[(size_t)t * a_stride + e])) + dt_bias[e];
+      const float softplus = z > 20.f ? z : log1pf(expf(z));
+      row[C + e] = expf(-expf(A_log[e / unit_dim]) * softplus);
+    } else {
+      row[C + e] = 1.f / (1.f + expf(-to_f32(proj[(size_t)t * stride + beta_col + e - gate_channels])));
+    }
+  }
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int head = warp; head * unit_dim < unit_channels; head += nwarps) {
+  for (int c0 = c_lo + warp * unit_dim; c0 < min(c_hi, unit_channels); c0 += nwarps * unit_dim) {
     float ss = 0.f;
-    for (int i = lane; i < unit_dim; i += 32) ss += val[head * unit_dim + i] * val[head * unit_dim + i];
+    for (int i = lane; i < unit_dim; i += 32) ss += val[c0 - c_lo + i] * val[c0 - c_lo + i];
     ss = warp_sum(ss);
-    const float r = rsqrtf(ss + unit_eps) * (head * unit_dim < scaled_channels ? scale : 1.f);
-    for (int i = lane; i < unit_dim; i += 32) val[head * unit_dim + i] *= r;
+    const float r = rsqrtf(ss + unit_eps) * (c0 < scaled_channels ? scale : 1.f);
+    for (int i = lane; i < unit_dim; i += 32) val[c0 - c_lo + i] *= r;
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) row[c] = val[c];
+  for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) row[c] = val[c - c_lo];
 }
 
 extern "C" int omnia_short_conv(const void* proj, int stride, int col0, int channels, int taps_count,
@@ -96,14 +112,23 @@ extern "C" int omnia_short_conv(const void* proj, int stride, int col0, int chan
   if (taps_count < 1 || taps_count > DELTA_MAX_TAPS || ((unit_channels || gate_channels) && unit_dim < 1) ||
       out_stride < channels + gate_channels + beta_heads)
     return (int)cudaErrorInvalidValue;
-  const size_t smem = sizeof(float) * (size_t)channels;
+  // Few tokens: many small blocks a token, so that a decode step fills the GPU; many tokens: a
+  // block takes about a thousand channels, since a block that lives for one channel a thread
+  // costs more to start than to run.
+  const int threads = tokens <= 32 ? 128 : 256;
+  const int unit = unit_dim > 0 ? unit_dim : 1;
+  const int aim = tokens <= 32 ? 128 : 1024;
+  const int chunk = aim >= unit ? (aim / unit) * unit : unit;
+  const size_t smem = sizeof(float) * (size_t)chunk;
+  const dim3 grid(tokens, (channels + chunk - 1) / chunk);
   OMNIA_DISPATCH_DTYPE(dtype, {
     if (smem > 48 * 1024 &&
         cudaFuncSetAttribute(short_conv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return (int)cudaGetLastError();
-    launch_pdl(short_conv_kernel<T>, tokens, 256, smem, stream, (const T*)proj, stride, col0, channels, taps_count,
-               taps, state, cu_seqlens, state_slots, num_seqs, unit_channels, unit_dim, unit_eps, scaled_channels,
-               scale, (const T*)a_rows, a_stride, A_log, dt_bias, gate_channels, beta_col, beta_heads, y, out_stride);
+    launch_pdl(short_conv_kernel<T>, grid, dim3(threads), smem, stream, (const T*)proj, stride, col0, channels, taps_count,
+               taps, state, cu_seqlens, state_slots, num_seqs, unit_channels, unit, unit_eps, scaled_channels,
+               scale, (const T*)a_rows, a_stride, A_log, dt_bias, gate_channels, beta_col, beta_heads, y, out_stride,
+               chunk);
   });
   return OMNIA_LAUNCH_RESULT();
 }

@@ -54,15 +54,31 @@ __global__ void streams_enter_kernel(const float* __restrict__ xs, const float* 
   const bool again = mu != nullptr && !from_state;  // the row before is normed again
   float* u0 = rows;
   float* u1 = rows + D;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) {
-    float v = 0.f, p = 0.f;
-    for (int s = 0; s < S; ++s) {
-      v += a[s] * xs[((size_t)t * S + s) * D + i];
-      if (again) p += a[s] * xs[((size_t)(t - 1) * S + s) * D + i];
+  // All of a thread's loads are asked for before the first is used: the stream count is a loop
+  // bound the compiler knows, and four elements go side by side.
+  for (int i0 = threadIdx.x; i0 < D; i0 += 4 * blockDim.x) {
+    float v[4] = {0.f, 0.f, 0.f, 0.f}, p[4] = {0.f, 0.f, 0.f, 0.f};
+    float x[4][OMNIA_MAX_STREAMS], xp[4][OMNIA_MAX_STREAMS];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = i0 + e * blockDim.x;
+#pragma unroll
+      for (int s = 0; s < OMNIA_MAX_STREAMS; ++s) {
+        x[e][s] = (s < S && i < D) ? xs[((size_t)t * S + s) * D + i] : 0.f;
+        xp[e][s] = (again && s < S && i < D) ? xs[((size_t)(t - 1) * S + s) * D + i] : 0.f;
+      }
     }
-    u0[i] = v;
-    u1[i] = p;
-    if (sum_out != nullptr) sum_out[(size_t)t * D + i] = v;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = i0 + e * blockDim.x;
+#pragma unroll
+      for (int s = 0; s < OMNIA_MAX_STREAMS; ++s) v[e] += a[s] * x[e][s], p[e] += a[s] * xp[e][s];
+      if (i < D) {
+        u0[i] = v[e];
+        u1[i] = p[e];
+        if (sum_out != nullptr) sum_out[(size_t)t * D + i] = v[e];
+      }
+    }
   }
   __syncthreads();
 

@@ -1118,7 +1118,7 @@ def latent_split_plan(q_lens, heads: int, longest: int, rows_per_block: int, sms
     blocks = sum(-(-q * heads // rows_per_block) for q in q_lens)
     if blocks >= sms or longest <= 128:
         return 1, 0
-    splits = min(-(-2 * sms // blocks), -(-longest // 128))
+    splits = min(-(-2 * sms // blocks), -(-longest // 128), 256)
     chunk = -(-(-(-longest // splits)) // 32) * 32
     return -(-longest // chunk), chunk
 
