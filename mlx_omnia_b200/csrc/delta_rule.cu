@@ -63,19 +63,12 @@ __global__ void short_conv_kernel(const T* __restrict__ proj, int stride, int co
   float z_first = 0.f;
   if (threadIdx.x < per && e0 < gate_channels) z_first = to_f32(a_rows[(size_t)t * a_stride + e0]);
   for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) {
-    float x[DELTA_MAX_TAPS];
-#pragma unroll
-    for (int j = 0; j < DELTA_MAX_TAPS; ++j) {
-      if (j >= K) break;
-      const int src = t - (K - 1 - j);
-      x[j] = src >= start ? to_f32(proj[(size_t)src * stride + col0 + c])
-                          : tail[(size_t)(K - 1 - (start - src)) * C + c];
-    }
     float acc = 0.f;
-#pragma unroll
-    for (int j = 0; j < DELTA_MAX_TAPS; ++j) {
-      if (j >= K) break;
-      acc += taps[(size_t)c * K + j] * x[j];
+    for (int j = 0; j < K; ++j) {
+      const int src = t - (K - 1 - j);  // K - 1 - j tokens before t
+      const float x = src >= start ? to_f32(proj[(size_t)src * stride + col0 + c])
+                                   : tail[(size_t)(K - 1 - (start - src)) * C + c];
+      acc += taps[(size_t)c * K + j] * x;
     }
     val[c - c_lo] = acc / (1.f + expf(-acc));
   }

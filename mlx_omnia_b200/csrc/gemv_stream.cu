@@ -440,6 +440,19 @@ gemv_stream_kernel(const bf16* __restrict__ a, const __grid_constant__ CUtensorM
             const float z = __bfloat162float(__float2bfloat16_rn(v)) * multiplier;
             reinterpret_cast<float*>(out)[(size_t)token * n + col] = cap > 0.f ? cap * tanhf(z / cap) : z;
           } else {
+            // cap selects an activation of the stored product (0 none, 1 relu^2, 2 tanh-GELU, 3 SiLU),
+            // applied to the product as bfloat16 would hold it, as a separate kernel would read it.
+            if (cap != 0.f) {
+              const float z = __bfloat162float(__float2bfloat16_rn(v));
+              if (cap == 1.f) {
+                const float r = fmaxf(z, 0.f);
+                v = r * r;
+              } else if (cap == 2.f) {
+                v = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+              } else {
+                v = z / (1.f + expf(-z));
+              }
+            }
             reinterpret_cast<bf16*>(out)[(size_t)token * n + col] = __float2bfloat16_rn(v);
           }
         }
@@ -524,7 +537,7 @@ int launch_rows(const bf16* a, const bf16* w, void* out, int m, int n, int k, in
 
 }  // namespace
 
-// epilogue: 0 store bfloat16 [m, n]; 1 SwiGLU, w = [gate rows | up rows] with n = 2 * inner,
+// epilogue: 0 store bfloat16 [m, n] (cap 1, 2, 3: relu^2, tanh-GELU or SiLU of the product; 0: as it is); 1 SwiGLU, w = [gate rows | up rows] with n = 2 * inner,
 // out bfloat16 [m, inner]; 2 soft cap, out float32 [m, n]. err: the device error word.
 extern "C" int omnia_gemv_stream(const void* a, const void* w, void* out, int m, int n, int k, int epilogue,
                                  float multiplier, float cap, int* err, cudaStream_t stream) {
@@ -540,8 +553,8 @@ extern "C" int omnia_gemv_stream(const void* a, const void* w, void* out, int m,
   }
   if (epilogue == EPI_SOFTCAP)
     return launch_rows<EPI_SOFTCAP, false>(ap, wp, out, m, n, k, 0, multiplier, cap, none, err, stream);
-  if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
-  return launch_rows<EPI_STORE, false>(ap, wp, out, m, n, k, 0, 1.f, 0.f, none, err, stream);
+  if (epilogue != EPI_STORE || cap < 0.f || cap > 3.f) return (int)cudaErrorInvalidValue;
+  return launch_rows<EPI_STORE, false>(ap, wp, out, m, n, k, 0, 1.f, cap, none, err, stream);
 }
 
 extern "C" int omnia_gemv_stream_pending_max_k(void) { return PENDING_MAX_K; }

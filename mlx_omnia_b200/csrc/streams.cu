@@ -3,6 +3,7 @@
 //
 //   enter:  u = sum_s a[s] x_s;  n = grouped_rms(u) * w;  h = n + (n_prev - n) * mu     (mu optional)
 //   leave:  x_t <- sum_s M[s, t] x_s + b[t] * y    for all t at once                    (M, b optional: x += y)
+//           and, when asked, the entry of the branch that follows (without a shift) from the new x
 //
 // x is float32 [tokens, S, D] (S = 1: the plain residual). One block per token. All arithmetic is
 // float32; only h and y have the engine's element type. The order of every sum depends on the
@@ -28,6 +29,52 @@ __device__ __forceinline__ int request_of(const int* __restrict__ cu_seqlens, in
   return lo;
 }
 
+// h = grouped_rms(u0) * w, shifted towards the row before when mu is given (that row is u1, normed
+// here too, or `prev_row` as it stands). u0, u1: shared memory [D]; part: shared [2][32].
+// A team of W warps per group; teams take the groups in turn; every sum in a fixed order.
+template <typename T>
+__device__ __forceinline__ void grouped_norm_store(const float* u0, const float* u1, int D, int groups,
+                                                   const float* __restrict__ w, float eps,
+                                                   const float* __restrict__ mu, bool from_state,
+                                                   const float* __restrict__ prev_row, float* __restrict__ last_row,
+                                                   T* __restrict__ h_row, float (*part)[32]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int W = groups < nwarps ? nwarps / groups : 1;
+  const int teams = nwarps / W;
+  const int team = warp / W, wi = warp % W;
+  const int gs = D / groups;
+  for (int g0 = 0; g0 < groups; g0 += teams) {
+    const int g = g0 + team;
+    const bool active = team < teams && g < groups;
+    float s0 = 0.f, s1 = 0.f;
+    if (active) {
+      for (int i = g * gs + wi * 32 + lane; i < (g + 1) * gs; i += W * 32) {
+        s0 += u0[i] * u0[i];
+        if (mu != nullptr) s1 += u1[i] * u1[i];
+      }
+    }
+    s0 = warp_sum(s0);
+    s1 = warp_sum(s1);
+    __syncthreads();
+    if (lane == 0) part[0][warp] = s0, part[1][warp] = s1;
+    __syncthreads();
+    if (!active) continue;
+    float t0 = 0.f, t1 = 0.f;
+    for (int j = 0; j < W; ++j) t0 += part[0][team * W + j], t1 += part[1][team * W + j];
+    const float r0 = rsqrtf(t0 / (float)gs + eps), r1 = rsqrtf(t1 / (float)gs + eps);
+    for (int i = g * gs + wi * 32 + lane; i < (g + 1) * gs; i += W * 32) {
+      const float n = u0[i] * r0 * w[i];
+      float out = n;
+      if (mu != nullptr) {
+        const float before = from_state ? prev_row[i] : u1[i] * r1 * w[i];
+        out = n + (before - n) * mu[i];
+        if (last_row != nullptr) last_row[i] = n;
+      }
+      h_row[i] = from_f32<T>(out);
+    }
+  }
+}
+
 template <typename T>
 __global__ void streams_enter_kernel(const float* __restrict__ xs, const float* __restrict__ coef, int S, int D,
                                      const float* __restrict__ w, float eps, int groups,
@@ -40,7 +87,6 @@ __global__ void streams_enter_kernel(const float* __restrict__ xs, const float* 
   extern __shared__ float rows[];  // u of this token [D], u of the token before [D]
   __shared__ float part[2][32];
   const int t = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   float a[OMNIA_MAX_STREAMS];
 #pragma unroll
   for (int s = 0; s < OMNIA_MAX_STREAMS; ++s) a[s] = s < S ? (coef ? coef[s] : 1.f) : 0.f;
@@ -82,42 +128,9 @@ __global__ void streams_enter_kernel(const float* __restrict__ xs, const float* 
   }
   __syncthreads();
 
-  // A team of W warps per group; teams take the groups in turn.
-  const int W = groups < nwarps ? nwarps / groups : 1;
-  const int teams = nwarps / W;
-  const int team = warp / W, wi = warp % W;
-  const int gs = D / groups;
   const float* prev_row = (mu != nullptr && from_state) ? prev + (size_t)state_slots[seq] * D : nullptr;
-  for (int g0 = 0; g0 < groups; g0 += teams) {
-    const int g = g0 + team;
-    const bool active = team < teams && g < groups;
-    float s0 = 0.f, s1 = 0.f;
-    if (active) {
-      for (int i = g * gs + wi * 32 + lane; i < (g + 1) * gs; i += W * 32) {
-        s0 += u0[i] * u0[i];
-        s1 += u1[i] * u1[i];
-      }
-    }
-    s0 = warp_sum(s0);
-    s1 = warp_sum(s1);
-    __syncthreads();
-    if (lane == 0) part[0][warp] = s0, part[1][warp] = s1;
-    __syncthreads();
-    if (!active) continue;
-    float t0 = 0.f, t1 = 0.f;
-    for (int j = 0; j < W; ++j) t0 += part[0][team * W + j], t1 += part[1][team * W + j];
-    const float r0 = rsqrtf(t0 / (float)gs + eps), r1 = rsqrtf(t1 / (float)gs + eps);
-    for (int i = g * gs + wi * 32 + lane; i < (g + 1) * gs; i += W * 32) {
-      const float n = u0[i] * r0 * w[i];
-      float out = n;
-      if (mu != nullptr) {
-        const float before = from_state ? prev_row[i] : u1[i] * r1 * w[i];
-        out = n + (before - n) * mu[i];
-        if (is_last) last[(size_t)seq * D + i] = n;
-      }
-      h[(size_t)t * D + i] = from_f32<T>(out);
-    }
-  }
+  grouped_norm_store<T>(u0, u1, D, groups, w, eps, mu, from_state, prev_row, is_last ? last + (size_t)seq * D : nullptr,
+                        h + (size_t)t * D, part);
 }
 
 extern "C" int omnia_streams_enter(const float* xs, const float* coef, int streams, int width, const float* w,
@@ -143,9 +156,13 @@ template <typename T>
 __global__ void streams_leave_kernel(float* __restrict__ xs, const T* __restrict__ y, const float* __restrict__ mix,
                                      const float* __restrict__ outc, int S, int D, int tokens,
                                      const float* __restrict__ last, float* __restrict__ prev,
-                                     const int* __restrict__ state_slots) {
+                                     const int* __restrict__ state_slots, const float* __restrict__ next_coef,
+                                     const float* __restrict__ next_w, float next_eps, int next_groups,
+                                     T* __restrict__ next_h) {
   pdl_wait();
   pdl_launch_dependents();
+  extern __shared__ float rows[];  // [D] when the next branch is entered here
+  __shared__ float part[2][32];
   const int t = blockIdx.x;
   if (t >= tokens) {
     const int seq = t - tokens;
@@ -163,6 +180,7 @@ __global__ void streams_leave_kernel(float* __restrict__ xs, const T* __restrict
     for (int s = 0; s < OMNIA_MAX_STREAMS; ++s)
       if (s < S) old[s] = xs[((size_t)t * S + s) * D + i];
     const float branch = to_f32(y[(size_t)t * D + i]);
+    float next_u = 0.f;
 #pragma unroll
     for (int to = 0; to < OMNIA_MAX_STREAMS; ++to) {
       if (to >= S) break;
@@ -170,18 +188,35 @@ __global__ void streams_leave_kernel(float* __restrict__ xs, const T* __restrict
 #pragma unroll
       for (int s = 0; s < OMNIA_MAX_STREAMS; ++s)
         if (s < S) v += m[s * S + to] * old[s];
-      xs[((size_t)t * S + to) * D + i] = v + m[OMNIA_MAX_STREAMS * OMNIA_MAX_STREAMS + to] * branch;
+      const float fresh = v + m[OMNIA_MAX_STREAMS * OMNIA_MAX_STREAMS + to] * branch;
+      xs[((size_t)t * S + to) * D + i] = fresh;
+      next_u += (next_coef ? next_coef[to] : 1.f) * fresh;
     }
+    if (next_h != nullptr) rows[i] = next_u;
   }
+  if (next_h == nullptr) return;
+  // The branch after this one reads the new streams: its entry (sum, grouped norm, weight; no
+  // token shift) is done here, while the row is still at hand.
+  __syncthreads();
+  grouped_norm_store<T>(rows, rows, D, next_groups, next_w, next_eps, nullptr, false, nullptr, nullptr,
+                        next_h + (size_t)t * D, part);
 }
 
 extern "C" int omnia_streams_leave(float* xs, const void* y, const float* mix, const float* outc, int streams,
                                    int width, int tokens, const float* last, float* prev, const int* state_slots,
-                                   int commits, int dtype, cudaStream_t stream) {
+                                   int commits, const float* next_coef, const float* next_w, float next_eps,
+                                   int next_groups, void* next_h, int dtype, cudaStream_t stream) {
   if (tokens + commits == 0) return 0;
   if (streams < 1 || streams > OMNIA_MAX_STREAMS || (mix == nullptr && streams != 1)) return (int)cudaErrorInvalidValue;
-  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(streams_leave_kernel<T>, tokens + commits, 256, 0, stream, xs, (const T*)y,
-                                          mix, outc, streams, width, tokens, last, prev, state_slots)));
+  if (next_h != nullptr && (next_groups < 1 || width % next_groups != 0 || next_w == nullptr)) return (int)cudaErrorInvalidValue;
+  const size_t smem = next_h != nullptr ? sizeof(float) * (size_t)width : 0;
+  OMNIA_DISPATCH_DTYPE(dtype, {
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(streams_leave_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return (int)cudaGetLastError();
+    launch_pdl(streams_leave_kernel<T>, tokens + commits, 256, smem, stream, xs, (const T*)y, mix, outc, streams, width,
+               tokens, last, prev, state_slots, next_coef, next_w, next_eps, next_groups, (T*)next_h);
+  });
   return OMNIA_LAUNCH_RESULT();
 }
 

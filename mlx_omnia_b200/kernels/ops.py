@@ -979,17 +979,23 @@ def streams_enter(xs: torch.Tensor, coef: torch.Tensor | None, streams: int, wei
 
 def streams_leave(xs: torch.Tensor, branch: torch.Tensor, mix: torch.Tensor | None, out: torch.Tensor | None,
                   streams: int, step: StepContext | None = None, last: torch.Tensor | None = None,
-                  prev: torch.Tensor | None = None) -> None:
+                  prev: torch.Tensor | None = None, enter: tuple | None = None) -> torch.Tensor | None:
     """In place: xs[:, t] = sum_s mix[s, t] xs[:, s] + out[t] * branch for all t at once (`mix` None with
     one stream: xs += branch). With `last` and `prev`, every request's row of `last` is also copied
-    into its state slot of `prev` (the token shift's commit)."""
+    into its state slot of `prev` (the token shift's commit). With `enter` = (coef, weight, eps,
+    groups) the entry of the branch that follows (`streams_enter` without a shift) is done in the
+    same kernel from the new streams, and its h is returned."""
     tokens, width = xs.shape[0], xs.shape[1] // streams
     commits = step.num_seqs if last is not None else 0
+    h = torch.empty(tokens, width, dtype=branch.dtype, device=xs.device) if enter is not None else None
+    coef, weight, eps, groups = enter if enter is not None else (None, None, 0.0, 1)
     fn = _function("streams", "omnia_streams_leave",
                    [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                    c_int, c_void_p])
+                    c_void_p, c_void_p, c_float, c_int, c_void_p, c_int, c_void_p])
     _check(fn(_ptr(xs), _ptr(branch), _ptr(mix), _ptr(out), streams, width, tokens, _ptr(last), _ptr(prev),
-              _ptr(step.state_slots) if commits else None, commits, _code(branch.dtype), _stream()), "streams_leave")
+              _ptr(step.state_slots) if commits else None, commits, _ptr(coef), _ptr(weight), eps, groups, _ptr(h),
+              _code(branch.dtype), _stream()), "streams_leave")
+    return h
 
 
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
@@ -1001,6 +1007,15 @@ def activation(z: torch.Tensor, kind: str) -> torch.Tensor:
     fn = _function("elementwise", "omnia_activation", [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p])
     _check(fn(_ptr(z), _ptr(act), z.numel(), ACTIVATIONS[kind], _code(z.dtype), _stream()), "activation")
     return act
+
+
+def linear_act(a: torch.Tensor, weight: torch.Tensor, kind: str) -> torch.Tensor:
+    """act(a @ weight^T): a few bfloat16 rows run on the weight-streaming kernel with the activation
+    in its epilogue; otherwise the library's product and the activation kernel."""
+    if _skinny(a, weight):
+        out = torch.empty(a.shape[0], weight.shape[0], dtype=a.dtype, device=a.device)
+        return _gemv_stream(a, weight, out, 0, 1.0, float(ACTIVATIONS[kind] + 1))
+    return activation(_library_mm(a, weight), kind)
 
 
 # ------------------------------------------------------------------------------------
@@ -1036,13 +1051,15 @@ def short_conv(proj: torch.Tensor, col0: int, channels: int, taps: torch.Tensor,
     return y
 
 
-def delta_parts(requests: int, heads: int, dv: int, sms: int) -> int:
+def delta_parts(requests: int, heads: int, dv: int, sms: int, longest: int = 1 << 30) -> int:
     """Into how many runs of columns the recurrence kernel cuts a head's value channels: 1 (the block
     then also norms the head's output) when the step's (request, head) pairs give half the SMs a block
-    each; otherwise the fewest equal runs (of a multiple of 4 columns, at least 16) that give every SM
-    about two blocks."""
+    each, or when no request brings more than 16 tokens (a decode step: measured at 8 requests of 8
+    heads, 17 us whole against 37 us cut, which pays a second kernel and eight loads of q, k and the
+    decays for one token); otherwise the fewest equal runs (of a multiple of 4 columns, at least 16)
+    that give every SM about two blocks."""
     blocks = requests * heads
-    if 2 * blocks >= sms:
+    if 2 * blocks >= sms or longest <= 16:
         return 1
     best = 1
     for parts in range(1, dv + 1):
@@ -1065,7 +1082,7 @@ def delta_rule(conv: torch.Tensor, channels: int, groups: int, heads: int, dk: i
     tokens = proj.shape[0]
     out = torch.empty(tokens, heads * dv, dtype=proj.dtype, device=proj.device)
     if parts is None:
-        parts = delta_parts(step.num_seqs, heads, dv, sm_count(proj.device))
+        parts = delta_parts(step.num_seqs, heads, dv, sm_count(proj.device), step.max_q_len)
     raw = torch.empty(tokens, heads * dv, dtype=torch.float32, device=proj.device) if parts > 1 else None
     fn = _function("delta_rule", "omnia_delta_rule",
                    [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,

@@ -199,11 +199,15 @@ class HyperPreNormBlock(Block):
             prev = ctx.block_state["shift"]
             last = torch.empty(step.num_seqs, self.hidden, dtype=torch.float32, device=x.device)
         h1 = ops.streams_enter(x, a_in, n, norm.weight, norm.eps, norm.groups, dtype, step, self.mu, prev, last)
-        ops.streams_leave(x, self.mixer.forward(h1, ctx), a_mix, a_out, n, step, last, prev)
-        if self.feed_forward is not None:
+        branch = self.mixer.forward(h1, ctx)
+        if self.feed_forward is None:
+            ops.streams_leave(x, branch, a_mix, a_out, n, step, last, prev)
+        else:
+            # Leaving the mixer's branch and entering the feed-forward's is one pass over the row.
             norm = self.norms["norm2"]
             b_in, b_mix, b_out = self.hc["hc2"]
-            h2 = ops.streams_enter(x, b_in, n, norm.weight, norm.eps, norm.groups, dtype)
+            h2 = ops.streams_leave(x, branch, a_mix, a_out, n, step, last, prev,
+                                   enter=(b_in, norm.weight, norm.eps, norm.groups))
             ops.streams_leave(x, self.feed_forward.forward(h2, ctx), b_mix, b_out, n)
         if exit_norm is None:
             return x, None

@@ -62,4 +62,4 @@ class DenseMLP(FeedForward):
         self.up, self.down = tensors["up"].contiguous(), tensors["down"].contiguous()
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
-        return ops.linear(ops.activation(ops.linear(h, self.up), self.activation), self.down)
+        return ops.linear(ops.linear_act(h, self.up, self.activation), self.down)

@@ -74,7 +74,14 @@ class ChannelDelta(Mixer):
             rows.append(torch.zeros(8 - total % 8, self.hidden, dtype=rows[0].dtype, device=rows[0].device))
         self.in_proj = torch.cat(rows, dim=0).contiguous()
         self.taps = torch.cat([tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]], dim=0).contiguous()
-        self.a2, self.g2, self.o = tensors["a2"].contiguous(), tensors["g2"].contiguous(), tensors["o"].contiguous()
+        # The second halves of the two low-rank maps as one block-diagonal operand: [a1 | g1] of the
+        # projected rows goes in, [decay logits | gate logits] comes out (the zeros add nothing).
+        a2, g2 = tensors["a2"], tensors["g2"]
+        self.second = torch.zeros(a2.shape[0] + g2.shape[0], self.decay_rank + self.gate_rank, dtype=a2.dtype,
+                                  device=a2.device)
+        self.second[: a2.shape[0], : self.decay_rank] = a2
+        self.second[a2.shape[0]:, self.decay_rank:] = g2
+        self.o = tensors["o"].contiguous()
         self.A_log, self.dt_bias = tensors["A_log"].contiguous(), tensors["dt_bias"].contiguous()
         self.norm_weight = tensors["norm"].contiguous()
 
@@ -82,8 +89,8 @@ class ChannelDelta(Mixer):
         step, state = ctx.step, ctx.state
         proj = ops.linear(h, self.in_proj)
         qk = self.kv_heads * self.dim
-        decay = ops.linear(proj[:, self.a1_col: self.a1_col + self.decay_rank], self.a2)
-        gate = ops.linear(proj[:, self.g1_col: self.g1_col + self.gate_rank], self.g2)
+        both = ops.linear(proj[:, self.a1_col: self.g1_col + self.gate_rank], self.second)
+        decay, gate = both[:, : self.heads * self.dim], both[:, self.heads * self.dim:]
         conv = ops.short_conv(proj, 0, self.channels, self.taps, state["conv"], step, 2 * qk, self.dim, self.unit_eps,
                               qk, self.dim ** -0.5, decay, self.A_log, self.dt_bias, self.beta_col, self.heads)
         out = ops.delta_rule(conv, self.channels, self.kv_heads, self.heads, self.dim, self.vdim, proj, 0, gate,

@@ -88,6 +88,13 @@ def test_streams_norm_and_shift(streams, groups, width):
         assert rel(torch.cat(got_h[r]), expect_h[r]) < 1e-5
         assert rel(torch.cat(got_x[r]), expect_x[r]) < 1e-5
     assert float((prev[[0, 2, 4]] - 9.0).abs().max()) == 0.0  # other requests' slots are left alone
+    # leaving one branch and entering the next in one kernel
+    x = torch.cat(xs).reshape(-1, streams * width).to(CUDA).contiguous()
+    h2 = ops.streams_leave(x, torch.cat(ys).to(CUDA), mix.to(CUDA), outc.to(CUDA), streams,
+                           enter=(coef.to(CUDA), w.to(CUDA), 1e-5, groups))
+    new = torch.cat(expect_x)
+    expect_h2 = plain.grouped_rms_norm((new * coef.to(F64)[None, :, None]).sum(1), w.to(F64), 1e-5, groups)
+    assert rel(h2, expect_h2) < 1e-5 and rel(x.view(-1, streams, width), new) < 1e-5
 
 
 def test_plain_residual_is_one_stream_without_mixing():
