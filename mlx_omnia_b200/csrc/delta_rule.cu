@@ -238,6 +238,7 @@ __global__ void __launch_bounds__(MAX_THREADS) delta_rule_kernel(
     const float* gs = ks + TC * VROW;
     const float* vs = gs + TC * VROW;
     const float* bs = vs + TC * cols;
+#pragma unroll 2
     for (int tok = 0; tok < n; ++tok) {
       const float* gt = gs + tok * VROW + p * SEG;
       const float* kt = ks + tok * VROW + p * SEG;
@@ -381,7 +382,8 @@ extern "C" int omnia_delta_rule(const float* conv, int conv_stride, int C, int G
                vector_loads);                                                                                     \
   } while (0)
   OMNIA_DISPATCH_DTYPE(dtype, {
-    if (cols * 4 <= 512) OMNIA_DELTA_LAUNCH(4, 512);
+    if (cols * 4 <= 128) OMNIA_DELTA_LAUNCH(4, 128);
+    else if (cols * 4 <= 512) OMNIA_DELTA_LAUNCH(4, 512);
     else if (cols * 4 <= 1024) OMNIA_DELTA_LAUNCH(4, 1024);
     else if (cols * 2 <= 1024) OMNIA_DELTA_LAUNCH(2, 1024);
     else OMNIA_DELTA_LAUNCH(1, 1024);
