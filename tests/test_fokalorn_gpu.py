@@ -313,12 +313,17 @@ def test_engine_with_tensor_core_latent_attention(tmp_path):
     raw["layers"][1]["mixer"].update(heads=6, dim=32, rot_dim=32, kv_rank=64, vdim=24, rot={"base": 1000.0, "dims": 32})
     raw["layers"].append(fc.config("X")["layers"][1])
     raw, weights, engine = engine_for("Y", "bfloat16", page=16, tokens=1024, raw=raw)
-    ids = {"a": fc.prompt(150, raw["vocab"], 1), "b": fc.prompt(61, raw["vocab"], 2)}
+    ids = {"a": fc.prompt(150, raw["vocab"], 1), "b": fc.prompt(61, raw["vocab"], 2), "c": fc.prompt(20, raw["vocab"], 3)}
     trace = Trace()
     trace.step({"a": ids["a"][:97]})
     trace.step({"a": ids["a"][97:130], "b": ids["b"][:60]})
     for t in range(130, 150):
-        trace.step({"a": ids["a"][t: t + 1], **({"b": ids["b"][60:]} if t == 130 else {})}, end=["b"] if t == 130 else [])
+        portions = {"a": ids["a"][t: t + 1]}
+        if t == 130:
+            portions["b"] = ids["b"][60:]
+        if 132 <= t < 142:  # the same shape ten times over: such mixed steps come to run from a captured graph
+            portions["c"] = ids["c"][2 * (t - 132): 2 * (t - 131)]
+        trace.step(portions, end=["b"] if t == 130 else ["c"] if t == 141 else [])
     got = trace.run_engine(engine, tmp_path / "out", before_step=lambda e, record: poison_free_pages(e))
     for r in ids:
         positions, logits = stacked(got[r])
