@@ -16,7 +16,8 @@ in every entry of the group. Groups may differ in how many pages a request needs
 them (`KVSpec.stride`), so every count below is per group.
 
 A group with a window gives a page back as soon as every position in it is behind
-the window of all tokens still to come; its block-table entry becomes -1. All pages
+the window of all tokens still to come; its block-table entry becomes -1. Pages that hold
+one of the first `keep_first` positions of such a group are kept until the request ends. All pages
 return when the request ends. Freed pages are handed out again, last freed first.
 
 Beside the pages there are *state slots*: a request holds one slot number for its
@@ -110,7 +111,7 @@ class RequestCache:
 class CacheManager:
     def __init__(self, needs: list[CacheNeed], *, page_size: int, pages_per_group: int | dict[KVSpec, int],
                  max_requests: int, dtype: torch.dtype = torch.bfloat16, device: torch.device | str = "cpu",
-                 allocate: bool = True) -> None:
+                 allocate: bool = True, model_state: "dict | None" = None) -> None:
         if page_size < 1:
             raise ValueError("page_size must be at least 1")
         self.page_size = page_size
@@ -159,14 +160,21 @@ class CacheManager:
                     self.initial_state[entry] = need.initial_state.to(need.state.dtype).to(device)
             if getattr(need, "block_state", None):
                 self.block_state[entry] = {name: slots_of(spec) for name, spec in need.block_state.items()}
+        # State that belongs to the model and to no schedule entry (an embedding that looks at the token before).
+        self.model_state: dict[str, torch.Tensor] = \
+            {name: slots_of(spec) for name, spec in (model_state or {}).items()} if allocate else {}
         self.requests: dict[str, RequestCache] = {}
 
     def reset_slots(self, slots: list[int]) -> None:
         """Set the state of `slots` (of requests about to run their first step) to its start:
         the mixer's `initial_state()` where it gave one, zeros everywhere else."""
-        if not slots or not (self.state or self.block_state):
+        if not slots or not (self.state or self.block_state or self.model_state):
             return
         index = None
+        for tensor in self.model_state.values():
+            if index is None:
+                index = torch.as_tensor(slots, device=tensor.device)
+            tensor.index_fill_(0, index, 0)
         for entry in sorted(set(self.state) | set(self.block_state)):
             held = self.state.get(entry)
             tensors = list(held.values()) if isinstance(held, dict) else ([held] if held is not None else [])
@@ -258,7 +266,9 @@ class CacheManager:
                 continue
             dead_below = request.tokens - window + 1  # positions < this are never read again
             dead_rows = max(dead_below, 0) // group.spec.stride  # stored rows wholly below it
-            for index in range(min(len(table), dead_rows // self.page_size) - 1, -1, -1):
+            # Pages that hold any of the first `keep_first` positions stay for the request's whole life.
+            kept = -(-group.spec.stored(group.spec.keep_first) // self.page_size) if group.spec.keep_first else 0
+            for index in range(min(len(table), dead_rows // self.page_size) - 1, kept - 1, -1):
                 if table[index] < 0:
                     break  # everything below was given back earlier
                 group.pool.give(table[index])

@@ -1,5 +1,7 @@
-// Paged causal attention for any batch shape, head size (<= 256), page size and element
-// type: the kernel of the 32-bit path, and of sizes the tiled kernels refuse.
+// Paged causal attention for any batch shape, head sizes (<= 256; keys and values may differ in
+// width), page size and element type: the kernel of the 32-bit path, and of sizes the tiled kernels
+// refuse. A window may keep the request's first `keep_first` positions visible for good, and the
+// softmax's denominator may hold one more term exp(sink[head]) that has no key and no value.
 //
 // One warp per (token, query head). Keys are visited in chunks of 32 starting at the
 // lowest visible position; in a chunk every lane scores one key (a full dot product in
@@ -11,14 +13,17 @@
 template <typename T>
 __global__ void paged_attention_generic_kernel(
     const T* __restrict__ q,                // [tokens, nq, d]
-    const T* __restrict__ pages,            // [num_pages, 2, nkv, page_size, d]
+    const T* __restrict__ k_pages,          // key row: k_pages + page * page_stride + (kvh * page_size + off) * d
+    const T* __restrict__ v_pages,          // value row: v_pages + page * page_stride + (kvh * page_size + off) * dv
+    long long page_stride,
     const int* __restrict__ block_table,    // [num_seqs, max_pages]
     const int* __restrict__ cu_seqlens,     // [num_seqs + 1]
     const int* __restrict__ positions,      // [tokens]
     const T* __restrict__ gate, int gate_stride,  // gate[t * gate_stride + h * d + i], or null
-    T* __restrict__ out,                    // [tokens, nq * d]
-    int num_seqs, int max_pages, int num_pages, int nq, int nkv, int d, int page_size,
-    int window, float scale, int* err) {
+    T* __restrict__ out,                    // [tokens, nq * dv]
+    const float* __restrict__ sink,         // [nq] or null
+    int num_seqs, int max_pages, int num_pages, int nq, int nkv, int d, int dv, int page_size,
+    int window, int keep_first, float scale, int* err) {
   __shared__ float qs[4][256];
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -45,18 +50,22 @@ __global__ void paged_attention_generic_kernel(
   for (int k = 0; k < 8; ++k) acc[k] = 0.f;
   const int* table = block_table + (size_t)seq * max_pages;
 
-  for (int base = first; base <= pos; base += 32) {
+  // Two runs of keys: the kept first positions below the window, then the window itself.
+  const int kept = min(keep_first, first);
+  for (int run = 0; run < 2; ++run) {
+  const int run_lo = run == 0 ? 0 : first, run_hi = run == 0 ? kept - 1 : pos;
+  for (int base = run_lo; base <= run_hi; base += 32) {
     const int j = base + lane;
     float s = -INFINITY;
     long long vrow = -1;
-    if (j <= pos) {
+    if (j <= run_hi) {
       const int page = table[j / page_size];
       if (page < 0 || page >= num_pages) {
         atomicOr(err, OMNIA_ERR_PAGE);
       } else {
-        const long long krow = (((long long)page * 2) * nkv + kvh) * page_size + j % page_size;
-        vrow = krow + (long long)nkv * page_size;
-        const T* kp = pages + krow * d;
+        const long long in_page = (long long)kvh * page_size + j % page_size;
+        vrow = (long long)page * page_stride + in_page * dv;
+        const T* kp = k_pages + (long long)page * page_stride + in_page * d;
         float dot = 0.f;
         for (int i = 0; i < d; ++i) dot += qs[warp][i] * to_f32(kp[i]);
         s = dot;
@@ -70,28 +79,37 @@ __global__ void paged_attention_generic_kernel(
     m = m_new;
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] *= alpha;
-    const int count = min(32, pos - base + 1);
+    const int count = min(32, run_hi - base + 1);
     for (int jj = 0; jj < count; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const long long vr = __shfl_sync(0xffffffffu, vrow, jj);
       if (vr < 0) continue;
-      const T* vp = pages + vr * d;
+      const T* vp = v_pages + vr;
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const int i = lane + 32 * k;
-        if (i < d) acc[k] += pj * to_f32(vp[i]);
+        if (i < dv) acc[k] += pj * to_f32(vp[i]);
       }
     }
   }
+  }
+  if (sink != nullptr) {  // one more term of the denominator, with no value: the sum only
+    const float z = sink[head];
+    const float m_new = fmaxf(m, z);
+    const float alpha = m == -INFINITY ? 0.f : expf(m - m_new);
+    l = l * alpha + expf(z - m_new);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] *= alpha;
+  }
   const float inv = l > 0.f ? 1.f / l : 0.f;
-  T* orow = out + ((size_t)t * nq + head) * d;
+  T* orow = out + ((size_t)t * nq + head) * dv;
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const int i = lane + 32 * k;
-    if (i >= d) continue;
+    if (i >= dv) continue;
     float v = acc[k] * inv;
     if (gate != nullptr) {
-      const float g = to_f32(gate[(size_t)t * gate_stride + (size_t)head * d + i]);
+      const float g = to_f32(gate[(size_t)t * gate_stride + (size_t)head * dv + i]);
       v *= 1.f / (1.f + expf(-g));
     }
     orow[i] = from_f32<T>(v);
@@ -99,16 +117,17 @@ __global__ void paged_attention_generic_kernel(
 }
 
 extern "C" int omnia_paged_attention_generic(
-    const void* q, const void* pages, const int* block_table, const int* cu_seqlens,
-    const int* positions, const void* gate, int gate_stride, void* out, int tokens, int num_seqs,
-    int max_pages, int num_pages, int nq, int nkv, int d, int page_size, int window, float scale,
-    int dtype, int* err, cudaStream_t stream) {
+    const void* q, const void* k_pages, const void* v_pages, long long page_stride, const int* block_table,
+    const int* cu_seqlens, const int* positions, const void* gate, int gate_stride, void* out, const float* sink,
+    int tokens, int num_seqs, int max_pages, int num_pages, int nq, int nkv, int d, int dv, int page_size, int window,
+    int keep_first, float scale, int dtype, int* err, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  if (d > 256 || nkv <= 0 || nq % nkv != 0) return (int)cudaErrorInvalidValue;
+  if (d > 256 || dv > 256 || nkv <= 0 || nq % nkv != 0 || keep_first < 0 || (keep_first > 0 && window <= 0))
+    return (int)cudaErrorInvalidValue;
   dim3 grid(tokens, (nq + 3) / 4);
   OMNIA_DISPATCH_DTYPE(dtype, (paged_attention_generic_kernel<T><<<grid, 128, 0, stream>>>(
-                                  (const T*)q, (const T*)pages, block_table, cu_seqlens, positions,
-                                  (const T*)gate, gate_stride, (T*)out, num_seqs, max_pages,
-                                  num_pages, nq, nkv, d, page_size, window, scale, err)));
+                                  (const T*)q, (const T*)k_pages, (const T*)v_pages, page_stride, block_table,
+                                  cu_seqlens, positions, (const T*)gate, gate_stride, (T*)out, sink, num_seqs,
+                                  max_pages, num_pages, nq, nkv, d, dv, page_size, window, keep_first, scale, err)));
   return OMNIA_LAUNCH_RESULT();
 }

@@ -18,6 +18,11 @@
 // Keys and values are addressed row by row through the block table, so any page size
 // works. Rows outside the visible range are zero-filled in shared memory (never read
 // from the cache), which keeps stale or poisoned pages out of the arithmetic.
+//
+// Two options serve mixers with a sliding window that keeps a request's first positions, and with
+// a softmax sink: `keep_first` (positions below it stay visible behind the window; the block that
+// owns the window's first keys walks the kept keys' tiles ahead of its own) and `sink` (one float
+// per query head: exp(sink) is added to the head's denominator when a row is finished).
 #include "common.cuh"
 
 #ifndef HEAD_DIM
@@ -115,10 +120,13 @@ __device__ __forceinline__ const bf16* cache_row(const CacheRef& c, int pos, int
 //   ks, vs:  shared-memory tiles [NKEYS][ROW]
 //   key0:    absolute position of the tile's first key
 //   row_lo/row_hi[2]: visible key range of the warp's rows g and g + 8 (inclusive; lo > hi: none)
+//   keep:    keys below it are visible whatever row_lo says (up to row_hi) ...
+//   floor:   ... unless they lie below this (they were attended to in a tile of their own)
 template <int NKEYS>
 __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16* ks, const bf16* vs,
                                             int key0, const int* row_lo, const int* row_hi,
-                                            float sl2, float* m, float* l, float (*o)[4]) {
+                                            float sl2, float* m, float* l, float (*o)[4], int keep = 0,
+                                            int floor = 0) {
   const int lane = threadIdx.x & 31;
   const int t = lane & 3;
   constexpr int NT = NKEYS / 8;
@@ -145,7 +153,7 @@ __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16*
     for (int e = 0; e < 4; ++e) {
       const int key = key0 + 8 * j + 2 * t + (e & 1);
       const int r = e >> 1;
-      if (key < row_lo[r] || key > row_hi[r]) s[j][e] = -INFINITY;
+      if (key < floor || (key < row_lo[r] && key >= keep) || key > row_hi[r]) s[j][e] = -INFINITY;
       mx[r] = fmaxf(mx[r], s[j][e]);
     }
   }
@@ -225,7 +233,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
                          const int* __restrict__ seq_lens, const int* __restrict__ work,
                          const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out,
                          int max_pages, int num_pages, int nq, int nkv, int page_size, int window,
-                         float scale, int* err) {
+                         float scale, int keep_first, const float* __restrict__ sink, int* err) {
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [BM][ROW]
@@ -253,14 +261,18 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
 
   const int last = pos0 + tokens - 1;                                    // last key any row sees
   const int first = window > 0 ? max(0, pos0 - window + 1) : 0;          // first key any row sees
-  const int tile0 = first / BN, tiles = last / BN - tile0 + 1;
+  // The kept first positions that lie below every row's window come first, in tiles of their own.
+  const int kept = min(keep_first, first);
+  const int kept_tiles = (kept + BN - 1) / BN;
+  const int tile0 = first / BN, tiles = kept_tiles + last / BN - tile0 + 1;
+  auto tile_of = [&](int tile) { return tile < kept_tiles ? tile : tile0 + tile - kept_tiles; };
 
   auto load_tile = [&](int tile, int stage) {
     bf16* kt = kv + stage * 2 * BN * ROW;
     bf16* vt = kt + BN * ROW;
     const int key = tid >> 1, sub = tid & 1;
-    const int pos = (tile0 + tile) * BN + key;
-    const bool visible = pos >= first && pos <= last;
+    const int pos = tile_of(tile) * BN + key;
+    const bool visible = tile < kept_tiles ? pos < kept : (pos >= first && pos <= last);
     const bf16* kp = visible ? cache_row(cache, pos, 0, err) : nullptr;
     const bf16* vp = kp ? kp + (size_t)nkv * page_size * D : nullptr;
 #pragma unroll
@@ -297,10 +309,14 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
     if (tile == 0) load_q_fragments(qs + warp * 16 * ROW, qf);
     const bf16* kt = kv + (tile & 1) * 2 * BN * ROW;
     // A warp whose rows see nothing of this tile skips it (rows are ordered by position).
-    const int key0 = (tile0 + tile) * BN;
+    const int key0 = tile_of(tile) * BN;
     const int warp_last = pos0 + min(rows - 1, warp * 16 + 15) / GROUP;
-    if (warp * 16 < rows && key0 <= warp_last)
-      attend_tile<BN>(qf, kt, kt + BN * ROW, key0, row_lo, row_hi, sl2, m, l, o);
+    if (warp * 16 < rows && tile < kept_tiles) {
+      const int all[2] = {0, 0}, below[2] = {min(row_hi[0], kept - 1), min(row_hi[1], kept - 1)};
+      attend_tile<BN>(qf, kt, kt + BN * ROW, key0, all, below, sl2, m, l, o);
+    } else if (warp * 16 < rows && key0 <= warp_last) {
+      attend_tile<BN>(qf, kt, kt + BN * ROW, key0, row_lo, row_hi, sl2, m, l, o, keep_first, kept);
+    }
     __syncthreads();
   }
   cp_async_wait<0>();
@@ -317,9 +333,10 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
   for (int r = 0; r < 2; ++r) {
     const int row = warp * 16 + (lane >> 2) + 8 * r;
     if (row >= rows) continue;
-    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
     const size_t token = (size_t)(q_begin + tok0 + row / GROUP);
     const int head = kvh * GROUP + row % GROUP;
+    if (sink != nullptr && m[r] != -INFINITY) l[r] += exp2f(sink[head] * LOG2E - m[r] * sl2);
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
     bf16* dst = out + (token * nq + head) * D;
     const bf16* gp = gate ? gate + token * gate_stride + (size_t)head * D : nullptr;
 #pragma unroll
@@ -350,7 +367,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pa
 template <int H>
 __device__ __forceinline__ void combine_heads(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               size_t base, int max_chunks, int c0, int c1, const bf16* gate_row,
-                                              bf16* out_row, float* stage, int stage_floats) {
+                                              bf16* out_row, float* stage, int stage_floats,
+                                              const float* sink = nullptr) {
   const int lane = threadIdx.x & 31;
   constexpr int PER_LANE = (D + 31) / 32;
   float gate_v[H][PER_LANE];
@@ -406,6 +424,7 @@ __device__ __forceinline__ void combine_heads(const float* __restrict__ part_o, 
   }
 #pragma unroll
   for (int h = 0; h < H; ++h) {
+    if (sink != nullptr && mx[h] != -INFINITY) total[h] += exp2f(sink[h] * LOG2E - mx[h]);  // mx is in log2 units
     const float inv = total[h] > 0.f ? 1.f / total[h] : 0.f;
 #pragma unroll
     for (int k = 0; k < PER_LANE; ++k) {
@@ -449,7 +468,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
                         int* __restrict__ tickets, const bf16* __restrict__ gate, int gate_stride,
                         bf16* __restrict__ out, int chunk_keys, int max_chunks, int max_pages,
                         int num_pages, int nq, int nkv, int page_size, int window, float scale,
-                        const FusedQK fused, int* err) {
+                        const FusedQK fused, int keep_first, const float* __restrict__ sink, int* err) {
   // In the fused mode nothing up to the query fragments depends on the kernel before this one
   // (the lengths and tables were copied in before the step began, the keys and values of earlier
   // tokens were written in earlier steps), so the block's start and its first loads of the cache
@@ -470,11 +489,15 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     if (early) pdl_wait();
     return;
   }
+  // The chunk that holds the window's first key also takes the kept first positions below the
+  // window: their tiles come ahead of the chunk's own in the list the warps share out.
+  const int kept = chunk == first / chunk_keys ? min(keep_first, first) : 0;
+  const int kept_tiles = (kept + DECODE_BN - 1) / DECODE_BN;
   const size_t token = (size_t)cu_seqlens[seq];
   // The chunk's block-table entries are read once, up front: a tile's loads then never wait
   // for a table lookup. (Chunks of more than DECODE_TABLE pages read the table directly.)
   __shared__ int table_s[DECODE_TABLE];
-  const int page_lo = lo / page_size, page_hi = hi / page_size;
+  const int page_lo = kept > 0 ? 0 : lo / page_size, page_hi = hi / page_size;
   const int* table_row = block_table + (size_t)seq * max_pages;
   const bool staged = page_hi - page_lo < DECODE_TABLE;
   if (staged)
@@ -486,16 +509,21 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     zero_padding(kv + stage * 2 * DECODE_BN * ROW, 2 * DECODE_BN, lane, 32);
 
   // This warp's tiles: every WARPS-th of the chunk's, starting with its own number.
-  const int tile0 = lo / DECODE_BN + warp, all_tiles = hi / DECODE_BN - lo / DECODE_BN + 1;
+  const int all_tiles = kept_tiles + hi / DECODE_BN - lo / DECODE_BN + 1;
   const int tiles = (all_tiles - warp + WARPS - 1) / WARPS;
+  // Tile `tile` of this warp, as a tile of absolute key positions.
+  auto tile_of = [&](int tile) {
+    const int listed = warp + tile * WARPS;
+    return listed < kept_tiles ? listed : lo / DECODE_BN + listed - kept_tiles;
+  };
   // A tile's loads: lane l looks up the row of key l once; then the warp copies the tile in
   // flat order (consecutive lanes take consecutive 16-byte chunks of a row, so every
   // request covers whole 128-byte lines), fetching each row's address by shuffle.
   auto load_tile = [&](int tile, int stage) {
     bf16* kt = kv + stage * 2 * DECODE_BN * ROW;
     bf16* vt = kt + DECODE_BN * ROW;
-    const int p = (tile0 + tile * WARPS) * DECODE_BN + lane;
-    const bool visible = p >= lo && p <= hi;
+    const int p = tile_of(tile) * DECODE_BN + lane;
+    const bool visible = warp + tile * WARPS < kept_tiles ? p < kept : (p >= lo && p <= hi);
     const bf16* mine = visible ? cache_row(cache, p, 0, err) : nullptr;
     const size_t v_offset = (size_t)nkv * page_size * D;
 #pragma unroll
@@ -658,8 +686,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     }
     __syncwarp();
     bf16* kt = kv + (tile % STAGES) * 2 * DECODE_BN * ROW;
-    if (brings_new && (tile0 + tile * WARPS) == pos / DECODE_BN) {
-      const int row = pos - (tile0 + tile * WARPS) * DECODE_BN;
+    if (brings_new && tile_of(tile) == pos / DECODE_BN) {
+      const int row = pos - tile_of(tile) * DECODE_BN;
 #pragma unroll
       for (int i = 0; i < VW; ++i) {
         kt[row * ROW + lane * VW + i] = __float2bfloat16_rn(new_k[i]);
@@ -667,8 +695,12 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
       }
       __syncwarp();
     }
-    attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, (tile0 + tile * WARPS) * DECODE_BN, row_lo, row_hi,
-                           sl2, m, l, o);
+    if (warp + tile * WARPS < kept_tiles) {
+      const int all[2] = {0, 0}, below[2] = {min(row_hi[0], kept - 1), min(row_hi[1], kept - 1)};
+      attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, tile_of(tile) * DECODE_BN, all, below, sl2, m, l, o);
+    } else {
+      attend_tile<DECODE_BN>(qf, kt, kt + DECODE_BN * ROW, tile_of(tile) * DECODE_BN, row_lo, row_hi, sl2, m, l, o);
+    }
     __syncwarp();
     if (STAGES == 1) {  // the one stage is free again
       if (tile + 1 < tiles) load_tile(tile + 1, 0);
@@ -765,13 +797,13 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pag
     const int head = kvh * GROUP + r;
     combine_heads<TOGETHER>(part_o, part_ml, ((size_t)blockIdx.z * nq + head) * max_chunks, max_chunks, c0, c1,
                      gate ? gate + token * gate_stride + (size_t)head * D : nullptr, out + (token * nq + head) * D,
-                     reinterpret_cast<float*>(smem_raw), STAGE_FLOATS);
+                     reinterpret_cast<float*>(smem_raw), STAGE_FLOATS, sink ? sink + head : nullptr);
   }
   if (GROUP % TOGETHER) {
     const int head = kvh * GROUP + GROUP - 1;
     combine_heads<1>(part_o, part_ml, ((size_t)blockIdx.z * nq + head) * max_chunks, max_chunks, c0, c1,
                      gate ? gate + token * gate_stride + (size_t)head * D : nullptr, out + (token * nq + head) * D,
-                     reinterpret_cast<float*>(smem_raw), STAGE_FLOATS);
+                     reinterpret_cast<float*>(smem_raw), STAGE_FLOATS, sink ? sink + head : nullptr);
   }
   OMNIA_TRACE_BLOCK(7);
 }
@@ -790,9 +822,9 @@ extern "C" int omnia_attention_prefill_tc(const void* q, const void* pages, cons
                                           const int* work, int blocks, const void* gate,
                                           int gate_stride, void* out, int max_pages, int num_pages,
                                           int nq, int nkv, int page_size, int window, float scale,
-                                          int* err, cudaStream_t stream) {
+                                          int keep_first, const float* sink, int* err, cudaStream_t stream) {
   if (blocks == 0) return 0;
-  if (nq != nkv * GROUP) return (int)cudaErrorInvalidValue;
+  if (nq != nkv * GROUP || keep_first < 0 || (keep_first > 0 && window <= 0)) return (int)cudaErrorInvalidValue;
   const size_t smem = (size_t)(BM + 4 * BN) * ROW * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
@@ -803,7 +835,7 @@ extern "C" int omnia_attention_prefill_tc(const void* q, const void* pages, cons
   }
   launch_pdl(attention_prefill_kernel, dim3(blocks, nkv), 128, smem, stream, 
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate,
-      gate_stride, (bf16*)out, max_pages, num_pages, nq, nkv, page_size, window, scale, err);
+      gate_stride, (bf16*)out, max_pages, num_pages, nq, nkv, page_size, window, scale, keep_first, sink, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -825,8 +857,10 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
                                          int page_size, int window, float scale, int warps,
                                          const void* proj, int proj_stride, int q_col, int k_col, int v_col,
                                          float eps, const float* inv_freq, const long long* slot_mapping,
-                                         int spread, int* err, cudaStream_t stream) {
+                                         int spread, int keep_first, const float* sink, int* err,
+                                         cudaStream_t stream) {
   if (requests == 0) return 0;
+  if (keep_first < 0 || (keep_first > 0 && (window <= 0 || proj != nullptr))) return (int)cudaErrorInvalidValue;
   if (requests < 0 || nkv < 1 || nq != nkv * GROUP || chunk_keys <= 0 || chunk_keys % DECODE_BN != 0 ||
       max_chunks < 1 || max_pages < 1 || num_pages < 1 || page_size < 1 || (warps != 1 && warps != 4))
     return (int)cudaErrorInvalidValue;
@@ -870,17 +904,17 @@ extern "C" int omnia_attention_decode_tc(const void* q, const void* pages, const
     launch_pdl(attention_decode_kernel<1, DECODE_STAGES>, dim3(max_chunks, nkv, requests), 32, smem, stream,
         (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
         tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-        num_pages, nq, nkv, page_size, window, scale, fused, err);
+        num_pages, nq, nkv, page_size, window, scale, fused, keep_first, sink, err);
   else if (deep)
     launch_pdl(attention_decode_kernel<4, 2>, dim3(max_chunks, nkv, requests), 128, smem, stream,
         (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
         tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-        num_pages, nq, nkv, page_size, window, scale, fused, err);
+        num_pages, nq, nkv, page_size, window, scale, fused, keep_first, sink, err);
   else
     launch_pdl(attention_decode_kernel<4, 1>, dim3(max_chunks, nkv, requests), 128, smem, stream,
         (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
         tickets, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-        num_pages, nq, nkv, page_size, window, scale, fused, err);
+        num_pages, nq, nkv, page_size, window, scale, fused, keep_first, sink, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -974,7 +1008,7 @@ extern "C" int omnia_attention_decode_tc_static(const void* q, const void* pages
   launch_pdl(attention_decode_kernel<1, DECODE_STAGES>, dim3(max_chunks, nkv, requests), 32, smem, stream,
       (const bf16*)q, (const bf16*)pages, block_table, cu_seqlens, seq_lens, seq_ids, part_o, part_ml,
       ticket_area, (const bf16*)gate, gate_stride, (bf16*)out, chunk_keys, max_chunks, max_pages,
-      num_pages, nq, nkv, page_size, window, scale, FusedQK{}, err);
+      num_pages, nq, nkv, page_size, window, scale, FusedQK{}, 0, nullptr, err);
   e = cudaGetLastError();
   if (e != cudaSuccess) snprintf(static_error, sizeof static_error, "launch: %s", cudaGetErrorString(e));
   return (int)e;

@@ -40,6 +40,67 @@ extern "C" int omnia_embed_rmsnorm(const int* ids, const void* table, float* x, 
 }
 
 // ---------------------------------------------------------------------------------
+// Embedding with a hashed table of token pairs: x[t] = table[ids[t]] * scale + pairs[row], row =
+// (before * mul_prev + ids[t] * mul_cur) mod buckets, `before` being the token ahead of t in its
+// request, and row = buckets (the table's extra last row) at position 0. The token ahead of a
+// portion's first token is read from `prev` [slots] (by the request's state slot); the block of that
+// first token, having read it, leaves the portion's last token there. Rows of padding (position
+// < 0) are zero. One block per token.
+template <typename T>
+__global__ void embed_pair_kernel(const int* __restrict__ ids, const int* __restrict__ positions,
+                                  const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
+                                  int num_seqs, const T* __restrict__ table, const T* __restrict__ pairs,
+                                  int* __restrict__ prev, float* __restrict__ x, int hidden, int vocab,
+                                  long long buckets, long long mul_prev, long long mul_cur, float scale, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  float* out = x + (size_t)t * hidden;
+  const int pos = positions[t];
+  if (pos < 0) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = 0.f;
+    return;
+  }
+  int lo = 0, hi = num_seqs - 1;  // the request of this token: the last s with cu_seqlens[s] <= t
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_seqlens[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  const int begin = cu_seqlens[lo], end = cu_seqlens[lo + 1];
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, OMNIA_ERR_TOKEN_ID);
+    id = 0;
+  }
+  int before = 0;
+  if (t > begin) {
+    before = ids[t - 1];
+  } else {
+    const int slot = state_slots[lo];
+    before = prev[slot];
+    __syncthreads();  // every thread has read the slot before one of them writes it
+    if (threadIdx.x == 0) prev[slot] = ids[end - 1];
+  }
+  if (before < 0 || before >= vocab) before = 0;
+  const long long row = pos == 0 ? buckets : ((long long)before * mul_prev + (long long)id * mul_cur) % buckets;
+  const T* a = table + (size_t)id * hidden;
+  const T* b = pairs + (size_t)row * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_f32(a[i]) * scale + to_f32(b[i]);
+}
+
+extern "C" int omnia_embed_pair(const int* ids, const int* positions, const int* cu_seqlens, const int* state_slots,
+                                int num_seqs, const void* table, const void* pairs, int* prev, float* x, int tokens,
+                                int hidden, int vocab, long long buckets, long long mul_prev, long long mul_cur,
+                                float scale, int dtype, int* err, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (buckets < 1 || mul_prev < 0 || mul_cur < 0) return (int)cudaErrorInvalidValue;
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(embed_pair_kernel<T>, tokens, 256, 0, stream, ids, positions, cu_seqlens,
+                                          state_slots, num_seqs, (const T*)table, (const T*)pairs, prev, x, hidden,
+                                          vocab, buckets, mul_prev, mul_cur, scale, err)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
 // h = x * rsqrt(mean(x^2) + eps) * w   (w may be null: weightless). x is float32.
 template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
@@ -71,7 +132,8 @@ extern "C" int omnia_rmsnorm(const float* x, const float* w, void* h, int rows, 
 // The residual step of a block, in one pass over the row:
 //   a  = branch                      (optionally normed: a * rsqrt(mean a^2 + eps_b) * wb)
 //   x += a                           (float32, in place)
-//   h  = x * rsqrt(mean x^2 + eps_o) * wo   (optional; wo may be null)
+//   h  = x * rsqrt(mean x^2 + eps_o) * wo   (optional; wo may be null; norm_out == 2: h = x, only rounded
+//        to the element type, for whoever reads the residual itself)
 // The row is staged in shared memory as float32, so the branch is read once and x is
 // read and written once.
 template <typename T>
@@ -106,11 +168,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     ss += v * v;
   }
   if (!norm_out) return;
-  const float scale_o = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps_o);
+  const float scale_o = norm_out == 2 ? 1.f : rsqrtf(block_sum(ss, scratch) / (float)hidden + eps_o);
   T* out = h + (size_t)blockIdx.x * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = row[i] * scale_o;
-    if (wo) v *= wo[i];
+    if (wo && norm_out == 1) v *= wo[i];
     out[i] = from_f32<T>(v);
   }
 }
@@ -168,7 +230,7 @@ __global__ void add_rmsnorm_reg_kernel(float* __restrict__ x, const T* __restric
       Vec4<T>::load(br + i, a[it]);
       Vec4<float>::load(xr + i, xv[it]);
       if (norm_branch && wb) Vec4<float>::load(wb + i, gb[it]);
-      if (norm_out && wo) Vec4<float>::load(wo + i, go[it]);
+      if (norm_out == 1 && wo) Vec4<float>::load(wo + i, go[it]);
     }
   }
   float ss = 0.f;
@@ -192,7 +254,7 @@ __global__ void add_rmsnorm_reg_kernel(float* __restrict__ x, const T* __restric
     if (i < hidden) Vec4<float>::store(xr + i, xv[it]);
   }
   if (!norm_out) return;
-  const float scale_o = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps_o);
+  const float scale_o = norm_out == 2 ? 1.f : rsqrtf(block_sum(ss, scratch) / (float)hidden + eps_o);
   T* out = h + (size_t)blockIdx.x * hidden;
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
@@ -401,6 +463,96 @@ extern "C" int omnia_qk_norm_rope_store(const void* proj, int row_stride, int q_
 }
 
 // ---------------------------------------------------------------------------------
+// The general form of the step above, for a mixer whose projections have biases, whose head norms
+// have a weight (one vector of the head's size, shared by the heads), whose values are of another
+// width than its keys, and whose rotation may cover only the first `rot` dims of a head:
+// per head of a projected row, bias added, RMS norm with weight (q and k; eps < 0: none), rotation
+// of dims (i, i + rot / 2) by position * inv_freq[i]; q goes to q_out [tokens, nq, dk], k and v to
+// the token's slot of the cache: key row (head h) at k_pages + page * page_stride + (h * page_size
+// + offset) * dk, value row at v_pages + page * page_stride + (h * page_size + offset) * dv.
+// One warp per (token, head).
+template <typename T>
+__global__ void qkv_prepare_kernel(const T* __restrict__ proj, int row_stride, int q_col, int k_col, int v_col,
+                                   int nq, int nkv, int dk, int dv, const T* __restrict__ bias,
+                                   const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                                   const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
+                                   const long long* __restrict__ slot_mapping, T* __restrict__ q_out,
+                                   T* __restrict__ k_pages, T* __restrict__ v_pages, long long page_stride,
+                                   int page_size, long long num_slots, int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hs = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (hs >= nq + 2 * nkv) return;
+  const int kind = hs < nq ? 0 : (hs < nq + nkv ? 1 : 2);
+  const int head = kind == 0 ? hs : (kind == 1 ? hs - nq : hs - nq - nkv);
+  const int d = kind == 2 ? dv : dk;
+  const int col = (kind == 0 ? q_col : kind == 1 ? k_col : v_col) + head * d;
+  const T* src = proj + (size_t)t * row_stride + col;
+  const T* b = bias ? bias + col : nullptr;
+  T* dst;
+  if (kind == 0) {
+    dst = q_out + ((size_t)t * nq + head) * dk;
+  } else {
+    const long long slot = slot_mapping[t];
+    if (slot < 0) return;
+    if (slot >= num_slots) {
+      if (lane == 0) atomicOr(err, OMNIA_ERR_SLOT);
+      return;
+    }
+    const long long page = slot / page_size, off = slot % page_size;
+    dst = (kind == 1 ? k_pages : v_pages) + page * page_stride + ((long long)head * page_size + off) * d;
+  }
+  if (kind == 2) {
+    for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(to_f32(src[i]) + (b ? to_f32(b[i]) : 0.f));
+    return;
+  }
+  __shared__ float staged[4][256];
+  float* v = staged[warp];
+  const float* w = kind == 0 ? q_weight : k_weight;
+  float ss = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    const float a = to_f32(src[i]) + (b ? to_f32(b[i]) : 0.f);
+    v[i] = a;
+    ss += a * a;
+  }
+  float scale = 1.f;
+  if (eps >= 0.f) scale = rsqrtf(warp_sum(ss) / (float)d + eps);
+  __syncwarp();
+  if (eps >= 0.f)
+    for (int i = lane; i < d; i += 32) v[i] = v[i] * scale * (w ? w[i] : 1.f);
+  __syncwarp();
+  const int rhalf = inv_freq != nullptr ? rot / 2 : 0;
+  const float pos = (float)positions[t];
+  for (int i = lane; i < rhalf; i += 32) {
+    float s, c;
+    sincosf(pos * inv_freq[i], &s, &c);
+    const float a0 = v[i], a1 = v[i + rhalf];
+    dst[i] = from_f32<T>(a0 * c - a1 * s);
+    dst[i + rhalf] = from_f32<T>(a1 * c + a0 * s);
+  }
+  for (int i = 2 * rhalf + lane; i < d; i += 32) dst[i] = from_f32<T>(v[i]);
+}
+
+extern "C" int omnia_qkv_prepare(const void* proj, int row_stride, int q_col, int k_col, int v_col, int nq, int nkv,
+                                 int dk, int dv, const void* bias, const float* q_weight, const float* k_weight,
+                                 float eps, const float* inv_freq, int rot, const int* positions,
+                                 const long long* slot_mapping, void* q_out, void* k_pages, void* v_pages,
+                                 long long page_stride, int page_size, long long num_slots, int tokens, int dtype,
+                                 int* err, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (dk > 256 || dv > 256 || rot > dk || (rot & 1)) return (int)cudaErrorInvalidValue;
+  const int heads = nq + 2 * nkv;
+  dim3 grid(tokens, (heads + 3) / 4);
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(qkv_prepare_kernel<T>, grid, 128, 0, stream, (const T*)proj, row_stride, q_col,
+                                          k_col, v_col, nq, nkv, dk, dv, (const T*)bias, q_weight, k_weight, eps,
+                                          inv_freq, rot, positions, slot_mapping, (T*)q_out, (T*)k_pages, (T*)v_pages,
+                                          page_stride, page_size, num_slots, err)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
 // angles[i][t] = (cos, sin)(positions[t] * inv_freq[i]): what a product's epilogue that rotates its
 // own rows reads. It has a thread per row, so the tokens run along the table's rows: a warp's 32
 // threads then read 32 neighbours. The same expression as in the kernel above, so a row rotates
@@ -452,6 +604,35 @@ extern "C" int omnia_swiglu(const void* gu, void* act, int rows, int inner, int 
   const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
   OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(swiglu_kernel<T>, blocks, 256, 0, stream, 
                                   (const T*)gu, (T*)act, total, inner)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
+// The clamped gated unit: g = min(gu[t, i], limit), u = clamp(gu[t, inner + i], -limit, limit);
+// act[t, i] = g * sigmoid(alpha * g) * (u + 1), in float32, rounded once.
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ act, long long total, int inner,
+                                   float alpha, float limit) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const long long t = idx / inner;
+    const int i = (int)(idx - t * inner);
+    const float g = fminf(to_f32(gu[t * 2 * inner + i]), limit);
+    const float u = fminf(fmaxf(to_f32(gu[t * 2 * inner + inner + i]), -limit), limit);
+    act[idx] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  }
+}
+
+extern "C" int omnia_clamped_glu(const void* gu, void* act, int rows, int inner, float alpha, float limit, int dtype,
+                                 cudaStream_t stream) {
+  const long long total = (long long)rows * inner;
+  if (total == 0) return 0;
+  const long long most = 16LL * omnia_sm_count();
+  const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(clamped_glu_kernel<T>, blocks, 256, 0, stream, (const T*)gu, (T*)act, total,
+                                          inner, alpha, limit)));
   return OMNIA_LAUNCH_RESULT();
 }
 

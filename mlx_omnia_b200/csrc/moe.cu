@@ -1,0 +1,410 @@
+// A routed mixture of small gated feed-forward layers ("experts"), as kernels that never ask the
+// host which token went where:
+//
+//   route     per token: router logits in float32, softmax over all router outputs, choice by
+//             score + correction, the `top` largest; the weights are the scores themselves. Router
+//             outputs at or beyond `experts` name identity experts (they have no tensors).
+//   plan      one block: where each expert's rows begin in the sorted order, and the list of row
+//             tiles (expert, first row, rows) that the grouped products walk.
+//   scatter   per (token, choice): its place among its expert's rows.
+//   grouped products over the sorted rows, a tile of rows belonging to one expert:
+//             act = silu(h W_gate^T) * (h W_up^T) (the rows of h gathered through the sorted order),
+//             then out = act W_down^T.
+//   combine   per token: the weighted sum of its choices' rows in a fixed order (identity experts
+//             add the token's own input), rounded once.
+//
+// The products have two forms: float32 arithmetic on the ordinary cores for any element type (the
+// 32-bit path), and bfloat16 on the tensor cores (mma.sync m16n8k16, float32 accumulation).
+#include "common.cuh"
+
+#include <limits.h>
+
+namespace {
+
+constexpr int ROUTE_THREADS = 128;
+constexpr int TILE_ROWS = 64;  // rows of a tile of the grouped products
+
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
+                 int outputs, int experts, int hidden, int top, int* __restrict__ choice,
+                 float* __restrict__ weight, int* __restrict__ counts) {
+  pdl_wait();
+  pdl_launch_dependents();
+  extern __shared__ float route_s[];  // [outputs] scores, [outputs] choice scores
+  float* score = route_s;
+  float* pick = route_s + outputs;
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* row = h + (size_t)t * hidden;
+  for (int e = warp; e < outputs; e += ROUTE_THREADS / 32) {
+    const float* w = router + (size_t)e * hidden;
+    float dot = 0.f;
+    for (int i = lane; i < hidden; i += 32) dot += to_f32(row[i]) * w[i];
+    dot = warp_sum(dot);
+    if (lane == 0) score[e] = dot;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float top_z = -INFINITY;
+  for (int e = lane; e < outputs; e += 32) top_z = fmaxf(top_z, score[e]);
+  top_z = warp_max(top_z);
+  float sum = 0.f;
+  for (int e = lane; e < outputs; e += 32) sum += expf(score[e] - top_z);
+  sum = warp_sum(sum);
+  for (int e = lane; e < outputs; e += 32) {
+    const float s = expf(score[e] - top_z) / sum;
+    score[e] = s;
+    pick[e] = s + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    // The largest choice score not taken yet; of equal ones the lowest index. A row of NaNs still
+    // gets `top` different experts (the lowest indices).
+    float best = -INFINITY;
+    int best_e = INT_MAX, spare = INT_MAX;
+    for (int e = lane; e < outputs; e += 32) {
+      const float v = pick[e];
+      if (v == -INFINITY) continue;  // taken
+      spare = min(spare, e);
+      if (v > best || (v == best && e < best_e)) best = v, best_e = e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+      spare = min(spare, __shfl_xor_sync(0xffffffffu, spare, o));
+      if (other > best || (other == best && other_e < best_e)) best = other, best_e = other_e;
+    }
+    if (best_e == INT_MAX) best_e = spare;
+    if (lane == 0) {
+      choice[(size_t)t * top + k] = best_e;
+      weight[(size_t)t * top + k] = score[best_e];
+      if (best_e < experts) atomicAdd(counts + best_e, 1);
+      pick[best_e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// offsets [experts + 1]; tiles [max_tiles, 3] = (expert, first row, rows); tile_count [1];
+// counts and cursors are left zero for the launches that follow.
+__global__ void moe_plan_kernel(int* __restrict__ counts, int* __restrict__ cursors, int* __restrict__ offsets,
+                                int* __restrict__ tiles, int* __restrict__ tile_count, int experts, int max_tiles) {
+  pdl_wait();
+  pdl_launch_dependents();
+  extern __shared__ int plan_s[];  // [experts + 1] row offsets, [experts + 1] tile offsets
+  int* row0 = plan_s;
+  int* tile0 = plan_s + experts + 1;
+  if (threadIdx.x == 0) {
+    int rows = 0, listed = 0;
+    for (int e = 0; e < experts; ++e) {
+      row0[e] = rows, tile0[e] = listed;
+      rows += counts[e];
+      listed += (counts[e] + TILE_ROWS - 1) / TILE_ROWS;
+    }
+    row0[experts] = rows, tile0[experts] = listed;
+    *tile_count = min(listed, max_tiles);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = row0[e];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int rows = row0[e + 1] - row0[e];
+    for (int i = 0, at = tile0[e]; i * TILE_ROWS < rows && at < max_tiles; ++i, ++at) {
+      tiles[3 * at] = e;
+      tiles[3 * at + 1] = row0[e] + i * TILE_ROWS;
+      tiles[3 * at + 2] = min(TILE_ROWS, rows - i * TILE_ROWS);
+    }
+    counts[e] = 0;
+    cursors[e] = 0;
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// place[t * top + k] = the sorted row of the choice (-1: an identity expert); source[row] = t.
+__global__ void moe_scatter_kernel(const int* __restrict__ choice, const int* __restrict__ offsets,
+                                   int* __restrict__ cursors, int* __restrict__ place, int* __restrict__ source,
+                                   int pairs, int top, int experts) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= pairs) return;
+  const int e = choice[i];
+  if (e >= experts) {
+    place[i] = -1;
+    return;
+  }
+  const int row = offsets[e] + atomicAdd(cursors + e, 1);
+  place[i] = row;
+  source[row] = i / top;
+}
+
+// ---------------------------------------------------------------------------------
+// Grouped product on the ordinary cores, any element type, float32 arithmetic.
+//   a:     [rows, k]; row r of the sorted order reads a[source ? source[r] : r]
+//   w:     [experts, n_total, k]; DUAL: n_total = 2 n, gate rows then up rows
+//   out:   [sorted rows, n]; DUAL: silu(gate) * up
+// grid (max tiles, n / 64): a block owns 64 rows x 64 columns, 256 threads of 4 x 4.
+template <typename T, bool DUAL>
+__global__ void __launch_bounds__(256)
+moe_product_kernel(const T* __restrict__ a, const int* __restrict__ source, const T* __restrict__ w,
+                   T* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ tile_count,
+                   int n, int k) {
+  pdl_wait();
+  pdl_launch_dependents();
+  if ((int)blockIdx.x >= *tile_count) return;
+  constexpr int BK = 16;
+  __shared__ float As[BK][TILE_ROWS + 4], Bs[DUAL ? 2 : 1][BK][64 + 4];
+  __shared__ int src_row[TILE_ROWS];
+  const int expert = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int n0 = blockIdx.y * 64;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  if (tid < TILE_ROWS) src_row[tid] = tid < rows ? (source ? source[row0 + tid] : row0 + tid) : -1;
+  __syncthreads();
+  const T* we = w + (size_t)expert * (DUAL ? 2 : 1) * n * k;
+  float acc[DUAL ? 2 : 1][4][4];
+#pragma unroll
+  for (int d = 0; d < (DUAL ? 2 : 1); ++d)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[d][i][j] = 0.f;
+  for (int k0 = 0; k0 < k; k0 += BK) {
+    for (int i = tid; i < TILE_ROWS * BK; i += 256) {
+      const int r = i / BK, c = i % BK;
+      const int src = src_row[r];
+      As[c][r] = (src >= 0 && k0 + c < k) ? to_f32(a[(size_t)src * k + k0 + c]) : 0.f;
+    }
+    for (int i = tid; i < 64 * BK; i += 256) {
+      const int r = i / BK, c = i % BK;
+      const bool live = n0 + r < n && k0 + c < k;
+      Bs[0][c][r] = live ? to_f32(we[(size_t)(n0 + r) * k + k0 + c]) : 0.f;
+      if (DUAL) Bs[1][c][r] = live ? to_f32(we[(size_t)(n + n0 + r) * k + k0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float av[4], bv[DUAL ? 2 : 1][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int d = 0; d < (DUAL ? 2 : 1); ++d)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bv[d][j] = Bs[d][kk][tx * 4 + j];
+#pragma unroll
+      for (int d = 0; d < (DUAL ? 2 : 1); ++d)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[d][i][j] += av[i] * bv[d][j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = n0 + tx * 4 + j;
+      if (c >= n) continue;
+      float v = acc[0][i][j];
+      if (DUAL) v = v / (1.f + expf(-v)) * acc[1][i][j];
+      out[(size_t)(row0 + r) * n + c] = from_f32<T>(v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// The same grouped product in bfloat16 on the tensor cores. A block of four warps owns 64 rows x 64
+// columns; a warp 16 rows x 64 columns (x 2 with DUAL). Steps of 32 along k through a cp.async
+// double buffer; k % 8 == 0 and operands whose rows start on 16 bytes.
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const bf16* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool DUAL>
+__global__ void __launch_bounds__(128)
+moe_product_tc_kernel(const bf16* __restrict__ a, const int* __restrict__ source, const bf16* __restrict__ w,
+                      bf16* __restrict__ out, const int* __restrict__ tiles, const int* __restrict__ tile_count,
+                      int n, int k) {
+  pdl_wait();
+  pdl_launch_dependents();
+  if ((int)blockIdx.x >= *tile_count) return;
+  constexpr int BK = 32, ROW = BK + 8, PARTS = DUAL ? 2 : 1;
+  __shared__ __align__(16) bf16 As[2][TILE_ROWS][ROW];
+  __shared__ __align__(16) bf16 Bs[2][PARTS][64][ROW];
+  __shared__ int src_row[TILE_ROWS];
+  const int expert = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
+  const int n0 = blockIdx.y * 64;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < TILE_ROWS) src_row[tid] = tid < rows ? (source ? source[row0 + tid] : row0 + tid) : -1;
+  __syncthreads();
+  const bf16* we = w + (size_t)expert * PARTS * n * k;
+  auto load = [&](int k0, int stage) {
+    // 64 rows x 4 chunks of 16 bytes for A, and for each part of B: 128 threads, 2 rounds each.
+    for (int i = tid; i < TILE_ROWS * 4; i += 128) {
+      const int r = i >> 2, c = i & 3;
+      const int src = src_row[r];
+      const bool live = src >= 0 && k0 + c * 8 < k;
+      cp_async16(&As[stage][r][c * 8], live ? a + (size_t)src * k + k0 + c * 8 : a, live);
+#pragma unroll
+      for (int part = 0; part < PARTS; ++part) {
+        const bool liveb = n0 + r < n && k0 + c * 8 < k;
+        cp_async16(&Bs[stage][part][r][c * 8], liveb ? we + (size_t)(part * n + n0 + r) * k + k0 + c * 8 : w, liveb);
+      }
+    }
+  };
+  float acc[PARTS][8][4];
+#pragma unroll
+  for (int part = 0; part < PARTS; ++part)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[part][j][0] = acc[part][j][1] = acc[part][j][2] = acc[part][j][3] = 0.f;
+  const int steps = (k + BK - 1) / BK;
+  load(0, 0);
+  cp_async_commit();
+  const int mat = lane >> 3;
+  for (int step = 0; step < steps; ++step) {
+    if (step + 1 < steps) load((step + 1) * BK, (step + 1) & 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int stage = step & 1;
+#pragma unroll
+    for (int ks = 0; ks < BK / 16; ++ks) {
+      unsigned af[4];
+      ldmatrix_x4(af[0], af[1], af[2], af[3], &As[stage][warp * 16 + (mat & 1) * 8 + (lane & 7)][ks * 16 + (mat >> 1) * 8]);
+#pragma unroll
+      for (int part = 0; part < PARTS; ++part)
+#pragma unroll
+        for (int j2 = 0; j2 < 4; ++j2) {
+          unsigned b0, b1, b2, b3;
+          ldmatrix_x4(b0, b1, b2, b3, &Bs[stage][part][j2 * 16 + (mat >> 1) * 8 + (lane & 7)][ks * 16 + (mat & 1) * 8]);
+          mma_bf16(acc[part][2 * j2], af, b0, b1);
+          mma_bf16(acc[part][2 * j2 + 1], af, b2, b3);
+        }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = warp * 16 + g + 8 * half;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int c = n0 + 8 * j + 2 * t4 + e;
+        if (c >= n) continue;
+        float v = acc[0][j][2 * half + e];
+        if (DUAL) v = v / (1.f + expf(-v)) * acc[PARTS - 1][j][2 * half + e];
+        out[(size_t)(row0 + r) * n + c] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// y[t] = sum over the token's choices, in their order, of weight * (the choice's row of `rows`, or the
+// token's own input h[t] for an identity expert). One block per token.
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ rows, const T* __restrict__ h, const int* __restrict__ place,
+                                   const float* __restrict__ weight, T* __restrict__ y, int hidden, int top) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int p = place[(size_t)t * top + k];
+      const float v = p >= 0 ? to_f32(rows[(size_t)p * hidden + i]) : to_f32(h[(size_t)t * hidden + i]);
+      acc += weight[(size_t)t * top + k] * v;
+    }
+    y[(size_t)t * hidden + i] = from_f32<T>(acc);
+  }
+}
+
+}  // namespace
+
+extern "C" int omnia_moe_route(const void* h, const float* router, const float* correction, int tokens, int outputs,
+                               int experts, int hidden, int top, int* choice, float* weight, int* counts, int dtype,
+                               cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (top < 1 || top > outputs || experts < 0 || experts > outputs || outputs > 4096) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)outputs * 2 * sizeof(float);
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(moe_route_kernel<T>, tokens, ROUTE_THREADS, smem, stream, (const T*)h, router,
+                                          correction, outputs, experts, hidden, top, choice, weight, counts)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+extern "C" int omnia_moe_tile_rows() { return TILE_ROWS; }
+
+// After `route`: the sorted order (offsets, place, source) and the tile list of the grouped products.
+extern "C" int omnia_moe_plan(const int* choice, int* counts, int* cursors, int* offsets, int* tiles, int* tile_count,
+                              int* place, int* source, int tokens, int top, int experts, int max_tiles,
+                              cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (experts < 1 || experts > 4096) return (int)cudaErrorInvalidValue;
+  launch_pdl(moe_plan_kernel, 1, 256, (size_t)(experts + 1) * 2 * sizeof(int), stream, counts, cursors, offsets, tiles,
+             tile_count, experts, max_tiles);
+  const int pairs = tokens * top;
+  launch_pdl(moe_scatter_kernel, (pairs + 255) / 256, 256, 0, stream, choice, (const int*)offsets, cursors, place, source,
+             pairs, top, experts);
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// dual != 0: w holds [experts, 2 n, k] (gate rows, then up rows) and out = silu(gate) * up.
+extern "C" int omnia_moe_product(const void* a, const int* source, const void* w, void* out, const int* tiles,
+                                 const int* tile_count, int max_tiles, int n, int k, int dual, int dtype,
+                                 int tensor_cores, cudaStream_t stream) {
+  if (max_tiles == 0) return 0;
+  const dim3 grid(max_tiles, (n + 63) / 64);
+  if (tensor_cores) {
+    if (dtype != OMNIA_BF16 || k % 8 != 0 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
+    if (dual)
+      launch_pdl(moe_product_tc_kernel<true>, grid, 128, 0, stream, (const bf16*)a, source, (const bf16*)w, (bf16*)out,
+                 tiles, tile_count, n, k);
+    else
+      launch_pdl(moe_product_tc_kernel<false>, grid, 128, 0, stream, (const bf16*)a, source, (const bf16*)w, (bf16*)out,
+                 tiles, tile_count, n, k);
+    return OMNIA_LAUNCH_RESULT();
+  }
+  OMNIA_DISPATCH_DTYPE(dtype, {
+    if (dual)
+      launch_pdl(moe_product_kernel<T, true>, grid, 256, 0, stream, (const T*)a, source, (const T*)w, (T*)out, tiles,
+                 tile_count, n, k);
+    else
+      launch_pdl(moe_product_kernel<T, false>, grid, 256, 0, stream, (const T*)a, source, (const T*)w, (T*)out, tiles,
+                 tile_count, n, k);
+  });
+  return OMNIA_LAUNCH_RESULT();
+}
+
+extern "C" int omnia_moe_combine(const void* rows, const void* h, const int* place, const float* weight, void* y,
+                                 int tokens, int hidden, int top, int dtype, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(moe_combine_kernel<T>, tokens, 256, 0, stream, (const T*)rows, (const T*)h,
+                                          place, weight, (T*)y, hidden, top)));
+  return OMNIA_LAUNCH_RESULT();
+}

@@ -88,7 +88,8 @@ class Engine:
         self.cache_tokens = tokens
         pages = -(-tokens // args.page_size)
         self.cache = CacheManager(needs, page_size=args.page_size, pages_per_group=pages,
-                                  max_requests=args.max_requests, dtype=runtime.dtype, device=runtime.device)
+                                  max_requests=args.max_requests, dtype=runtime.dtype, device=runtime.device,
+                                  model_state=model.model_state())
         self.runner = StepRunner(model, self.cache, runtime, cuda_graphs=args.cuda_graphs)
 
     @property

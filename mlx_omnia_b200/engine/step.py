@@ -174,6 +174,7 @@ class StepRunner:
 
     def layer_contexts(self, step: StepContext) -> list[LayerContext]:
         cache = self.cache
+        step.model_state = cache.model_state or None
         contexts = []
         for entry, need in enumerate(cache.needs):
             kv = None

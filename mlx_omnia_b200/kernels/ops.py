@@ -13,6 +13,7 @@ from __future__ import annotations
 import ctypes
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
+import dataclasses
 from dataclasses import dataclass
 
 import numpy as np
@@ -132,6 +133,29 @@ def embed_rmsnorm(ids: torch.Tensor, table: torch.Tensor, eps: float | None) -> 
     return x
 
 
+def embed_pair(step: StepContext, table: torch.Tensor, pairs: torch.Tensor, prev: torch.Tensor, scale: float,
+               mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """x[t] = table[id_t] * scale + pairs[(id_before * mul_prev + id_t * mul_cur) mod buckets], with
+    buckets = rows of `pairs` - 1 and the extra last row for a request's first token. The token before a
+    portion's first one is read from `prev` (int32 [slots], by state slot), which then receives the
+    portion's last token. -> float32 [tokens, hidden]."""
+    tokens, (vocab, hidden) = step.token_ids.shape[0], table.shape
+    x = torch.empty(tokens, hidden, dtype=torch.float32, device=table.device)
+    fn = _function("elementwise", "omnia_embed_pair",
+                   [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                    c_int, c_longlong, c_longlong, c_longlong, c_float, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(step.token_ids), _ptr(step.positions), _ptr(step.cu_seqlens), _ptr(step.state_slots),
+              step.num_seqs, _ptr(table), _ptr(pairs), _ptr(prev), _ptr(x), tokens, hidden, vocab,
+              pairs.shape[0] - 1, mul_prev, mul_cur, scale, _code(table.dtype), _ptr(error_word(table.device)),
+              _stream()), "embed_pair")
+    return x
+
+
+def rounded_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 residual `x` as activations of `dtype` (x itself when that is float32)."""
+    return x if dtype == torch.float32 else x.to(dtype)
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, dtype: torch.dtype) -> torch.Tensor:
     """h = x * rsqrt(mean x^2 + eps) * weight, x float32 [rows, hidden] -> `dtype`."""
     rows, hidden = x.shape
@@ -142,10 +166,19 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, dtype: tor
 
 
 def add_rmsnorm(x: torch.Tensor, branch: torch.Tensor, branch_weight: torch.Tensor | None,
-                branch_eps: float | None, out_weight: torch.Tensor | None, out_eps: float | None) -> torch.Tensor | None:
+                branch_eps: float | None, out_weight: torch.Tensor | None, out_eps: float | None,
+                rounded: bool = False) -> torch.Tensor | None:
     """x += norm_b(branch) in place (float32), then h = norm_o(x) in branch's dtype.
-    `branch_eps is None` adds the branch as it is; `out_eps is None` returns no h."""
+    `branch_eps is None` adds the branch as it is; `out_eps is None` returns no h, unless `rounded`:
+    h is then the new x itself in branch's dtype (for a part that reads the residual unnormed)."""
     rows, hidden = x.shape
+    if rounded and out_eps is None:
+        h = torch.empty_like(branch)
+        fn = _function("elementwise", "omnia_add_rmsnorm",
+                       [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_float, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check(fn(_ptr(x), _ptr(branch), _ptr(branch_weight), branch_eps or 0.0, int(branch_eps is not None),
+                  None, 0.0, 2, _ptr(h), rows, hidden, _code(branch.dtype), _stream()), "add_rmsnorm")
+        return h
     h = torch.empty_like(branch) if out_eps is not None else None
     fn = _function("elementwise", "omnia_add_rmsnorm",
                    [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_float, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
@@ -173,6 +206,40 @@ def qk_norm_rope_store(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, n
               _ptr(kv.pages) if store else None, kv.page_size if store else 1,
               kv.pages.shape[0] * kv.page_size if store else 0, tokens, _code(proj.dtype),
               _ptr(error_word(proj.device)), _stream()), "qk_norm_rope_store")
+    return q
+
+
+def kv_layout(kv: KVView) -> tuple[int, int, int, int, int, int]:
+    """(address of the keys of page 0, of its values, elements from a page to the next, key/value
+    heads, key width, value width) of an attention cache: two rows `(heads, width)` a position, of
+    equal widths (pages [num_pages, 2, heads, page_size, width]) or not (pages [num_pages, elements])."""
+    (nkv, dk), (_, dv) = kv.spec.rows if kv.spec is not None else ((kv.pages.shape[2], kv.pages.shape[4]),) * 2
+    item = kv.pages.element_size()
+    base = kv.pages.data_ptr()
+    return base, base + nkv * dk * kv.page_size * item, nkv * (dk + dv) * kv.page_size, nkv, dk, dv
+
+
+def qkv_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, nq: int, dk: int, bias: torch.Tensor | None,
+                q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float | None,
+                inv_freq: torch.Tensor | None, positions: torch.Tensor, kv: KVView, store: bool) -> torch.Tensor:
+    """Per head of the projected rows: bias (the whole row's, [columns]), RMS norm with a weight of the
+    head's size (q and k), rotation of the first 2 * len(inv_freq) dims in half-split pairs; q out as
+    [tokens, nq, dk], and with `store` the keys and the values (of a width of their own) into the cache."""
+    tokens, stride = proj.shape
+    k_ptr, v_ptr, page_stride, nkv, kdim, dv = kv_layout(kv)
+    if kdim != dk:
+        raise KernelError(f"the cache keeps keys of {kdim}, the mixer makes keys of {dk}")
+    q = torch.empty(tokens, nq, dk, dtype=proj.dtype, device=proj.device)
+    rot = 0 if inv_freq is None else 2 * inv_freq.shape[0]
+    fn = _function("elementwise", "omnia_qkv_prepare",
+                   [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                    c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int,
+                    c_longlong, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(proj), stride, q_col, k_col, v_col, nq, nkv if store else 0, dk, dv, _ptr(bias), _ptr(q_weight),
+              _ptr(k_weight), -1.0 if eps is None else eps, _ptr(inv_freq), rot, _ptr(positions),
+              _ptr(kv.slot_mapping) if store else None, _ptr(q), k_ptr, v_ptr, page_stride, kv.page_size,
+              kv.pages.shape[0] * kv.page_size, tokens, _code(proj.dtype), _ptr(error_word(proj.device)), _stream()),
+           "qkv_prepare")
     return q
 
 
@@ -516,10 +583,19 @@ def decode_fusable(proj: torch.Tensor, nq: int, nkv: int, d: int, inv_freq: torc
 
 def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale: float,
                     gate: torch.Tensor | None = None, gate_col: int = 0,
-                    projection: Projection | None = None, wide: bool | None = None) -> torch.Tensor:
+                    projection: Projection | None = None, wide: bool | None = None,
+                    sink: torch.Tensor | None = None, window: int | None = -1,
+                    keep_first: int | None = None) -> torch.Tensor:
     """Causal (windowed) attention of this step's queries over the paged cache, the
     output multiplied by sigmoid(gate) when `gate` (the projected rows; the gate's
-    columns start at `gate_col`) is given.  -> [tokens, nq * d]
+    columns start at `gate_col`) is given.  -> [tokens, nq * dv]
+
+    `sink` (float32 [nq]) adds exp(sink[head]) to every row's denominator. A cache whose spec names
+    `keep_first` keeps that many first positions visible behind the window; `window` and `keep_first`,
+    when given, are the mixer's own and replace the cache's (a mixer that reads another's cache may
+    see less of it than is kept). Sink and kept positions are taken by the generic
+    and the mma.sync kernels (not by the tcgen05 ones); values of another width than the keys run on
+    the generic kernel.
 
     With `projection` (only where `decode_fusable` holds) q is not given: the kernel makes the
     queries and the new keys and values from the projected rows, and writes the latter to the cache.
@@ -533,19 +609,28 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
         q = projection.rows  # for its dtype and device only
     else:
         tokens, nq, d = q.shape
-    nkv = kv.pages.shape[2]
-    out = torch.empty(tokens, nq * d, dtype=q.dtype, device=q.device)
+    k_ptr, v_ptr, page_stride, nkv, _, dv = kv_layout(kv)
+    if window != -1 and (window or 0) != (kv.window or 0):
+        kv = dataclasses.replace(kv, window=window)
+    keep = kv.keep_first if keep_first is None else keep_first
+    if not kv.window:
+        keep = 0
+    out = torch.empty(tokens, nq * dv, dtype=q.dtype, device=q.device)
     gate_ptr = None if gate is None else gate.data_ptr() + gate_col * gate.element_size()
     gate_stride = 0 if gate is None else gate.shape[1]
     err = _ptr(error_word(q.device))
     max_pages, num_pages = kv.block_table.shape[1], kv.pages.shape[0]
-    if not tiled_attention_supported(q.dtype, nq, nkv, d):
+    if dv != d or not tiled_attention_supported(q.dtype, nq, nkv, d):
+        if projection is not None:
+            raise KernelError("the generic attention kernel takes queries, not projected rows")
         fn = _function("attention_generic", "omnia_paged_attention_generic",
-                       [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
-        _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.positions),
-                  gate_ptr, gate_stride, _ptr(out), tokens, step.num_seqs, max_pages, num_pages, nq, nkv, d,
-                  kv.page_size, kv.window or 0, scale, _code(q.dtype), err, _stream()), "paged_attention")
+                       [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                        c_int, c_float, c_int, c_void_p, c_void_p])
+        _check(fn(_ptr(q), k_ptr, v_ptr, page_stride, _ptr(kv.block_table), _ptr(step.cu_seqlens),
+                  _ptr(step.positions), gate_ptr, gate_stride, _ptr(out), _ptr(sink), tokens, step.num_seqs, max_pages,
+                  num_pages, nq, nkv, d, dv, kv.page_size, kv.window or 0, keep, scale, _code(q.dtype), err,
+                  _stream()), "paged_attention")
         return out
     defines = {"HEAD_DIM": d, "GROUP": nq // nkv}
     # Requests that bring a single token take the split-key decode kernel, in a decode-only step
@@ -564,7 +649,7 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
                        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_float, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
-                        c_int, c_void_p, c_void_p], defines)
+                        c_int, c_int, c_void_p, c_void_p, c_void_p], defines)
         p = projection
         fused = (None, 0, 0, 0, 0, -1.0, None, None) if p is None else (
             _ptr(p.rows), p.rows.shape[1], p.q_col, p.k_col, p.v_col, -1.0 if p.eps is None else p.eps,
@@ -572,10 +657,10 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
         _check(fn(None if p is not None else _ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens),
                   _ptr(step.seq_lens), _ptr(single), count, _ptr(part_o), _ptr(part_ml), _ptr(tickets), chunk,
                   max_chunks, gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size,
-                  kv.window or 0, scale, warps, *fused, 1, err, _stream()), "attention_decode")
+                  kv.window or 0, scale, warps, *fused, 1, keep, _ptr(sink), err, _stream()), "attention_decode")
         if step.decode_only or all(n == 1 for n in step.q_lens):
             return out
-    if tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
+    if sink is None and not keep and tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
         per_block = 128 // (nq // nkv)
         sms = sm_count(q.device)
         if wide is None:
@@ -610,10 +695,10 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
     work = _prefill_work(step, tokens_per_block, q.device)
     fn = _function("attention_tc", "omnia_attention_prefill_tc",
                    [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
-                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p], defines)
+                    c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p], defines)
     _check(fn(_ptr(q), _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens), _ptr(work),
               work.shape[0], gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv, kv.page_size,
-              kv.window or 0, scale, err, _stream()), "attention_prefill")
+              kv.window or 0, scale, keep, _ptr(sink), err, _stream()), "attention_prefill")
     return out
 
 
@@ -624,6 +709,16 @@ def swiglu(gu: torch.Tensor) -> torch.Tensor:
     act = torch.empty(rows, inner, dtype=gu.dtype, device=gu.device)
     fn = _function("elementwise", "omnia_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(gu), _ptr(act), rows, inner, _code(gu.dtype), _stream()), "swiglu")
+    return act
+
+
+def clamped_glu(gu: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
+    """g = min(gu[:, :inner], limit), u = clamp(gu[:, inner:], -limit, limit); act = g sigmoid(alpha g) (u + 1)."""
+    rows, two_inner = gu.shape
+    inner = two_inner // 2
+    act = torch.empty(rows, inner, dtype=gu.dtype, device=gu.device)
+    fn = _function("elementwise", "omnia_clamped_glu", [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p])
+    _check(fn(_ptr(gu), _ptr(act), rows, inner, alpha, limit, _code(gu.dtype), _stream()), "clamped_glu")
     return act
 
 
@@ -896,6 +991,16 @@ def linear_swiglu(a, gate_up: torch.Tensor) -> torch.Tensor:
     if _tensor_core(a, gate_up, FUSED_GATE_ROWS):
         return _gemm_tcgen05(a, gate_up, torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device), 1)
     return swiglu(_library_mm(a, gate_up))
+
+
+def linear_clamped_glu(a: torch.Tensor, gate_up: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
+    """g = min(a @ gate^T, limit), u = clamp(a @ up^T, -limit, limit); g sigmoid(alpha g) (u + 1), with
+    gate_up = [gate rows | up rows] -> [rows, inner]."""
+    if _skinny(a, gate_up):
+        gu = _gemv_stream(a, gate_up, torch.empty(a.shape[0], gate_up.shape[0], dtype=a.dtype, device=a.device), 0)
+    else:
+        gu = _library_mm(a, gate_up)
+    return clamped_glu(gu, alpha, limit)
 
 
 def linear_softcap(a: torch.Tensor, weight: torch.Tensor, multiplier: float, cap: float | None) -> torch.Tensor:
@@ -1199,3 +1304,82 @@ def batched_mm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None
                                       or torch.get_float32_matmul_precision() != "highest"):
         raise KernelError("the 32-bit path needs true float32 matrix products; TF32 is switched on")
     return torch.bmm(a, b) if out is None else torch.bmm(a, b, out=out)
+
+
+# ------------------------------------------------------------------------------------
+# Routed experts (csrc/moe.cu)
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, experts: int, top: int,
+              counts: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per row of `h`: float32 logits against `router` (float32 [outputs, hidden]), softmax over all
+    outputs, the `top` largest of score + correction; -> (choice int32 [rows, top], weight float32
+    [rows, top]: the chosen outputs' scores, not renormalised). Outputs at or beyond `experts` are identity experts; the
+    others are counted into `counts` (int32 [experts], zero before the call)."""
+    rows, hidden = h.shape
+    choice = torch.empty(rows, top, dtype=torch.int32, device=h.device)
+    weight = torch.empty(rows, top, dtype=torch.float32, device=h.device)
+    fn = _function("moe", "omnia_moe_route",
+                   [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                    c_void_p])
+    _check(fn(_ptr(h), _ptr(router), _ptr(correction), rows, router.shape[0], experts, hidden, top, _ptr(choice),
+              _ptr(weight), _ptr(counts), _code(h.dtype), _stream()), "moe_route")
+    return choice, weight
+
+
+MOE_TILE_ROWS = 64
+"""Rows of a tile of the grouped products (csrc/moe.cu)."""
+
+
+def moe_experts(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, gate_up: torch.Tensor,
+                down: torch.Tensor, top: int, step: StepContext | None = None,
+                tensor_cores: bool | None = None) -> torch.Tensor:
+    """A routed mixture of gated feed-forward experts over the rows of `h` [rows, hidden]:
+    y = sum over a row's `top` choices of score * expert(h), expert e being
+    down[e] (silu(gate_e h) * (up_e h)) with gate_up [experts, 2 inner, hidden] (gate rows, then up
+    rows) and down [experts, hidden, inner]; router outputs beyond the experts with tensors are
+    identity experts (their output is h). Nothing is asked of the host: rows are sorted by expert on
+    the device, and the grouped products walk a tile list made there. bfloat16 runs on the tensor
+    cores (`tensor_cores` False keeps it off), float32 on the ordinary ones."""
+    rows, hidden = h.shape
+    experts, inner = gate_up.shape[0], gate_up.shape[1] // 2
+    pairs = rows * top
+    max_tiles = min(pairs, -(-pairs // MOE_TILE_ROWS) + experts)
+    device = h.device
+    if step is None:
+        step = _NoStep()
+    counts, cursors = _step_buffers(step, device, {"moe_counts": (experts, torch.int32, True),
+                                                   "moe_cursors": (experts, torch.int32, True)})
+    choice, weight = moe_route(h, router, correction, experts, top, counts)
+    ints = torch.empty(2 * pairs + experts + 1 + 3 * max_tiles + 1, dtype=torch.int32, device=device)
+    place, source = ints[:pairs], ints[pairs: 2 * pairs]
+    offsets = ints[2 * pairs: 2 * pairs + experts + 1]
+    tiles = ints[2 * pairs + experts + 1: 2 * pairs + experts + 1 + 3 * max_tiles]
+    tile_count = ints[-1:]
+    fn = _function("moe", "omnia_moe_plan",
+                   [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                    c_int, c_void_p])
+    _check(fn(_ptr(choice), _ptr(counts), _ptr(cursors), _ptr(offsets), _ptr(tiles), _ptr(tile_count), _ptr(place),
+              _ptr(source), rows, top, experts, max_tiles, _stream()), "moe_plan")
+    if tensor_cores is None:
+        tensor_cores = h.dtype == torch.bfloat16 and hidden % 8 == 0 and inner % 8 == 0
+    product = _function("moe", "omnia_moe_product",
+                        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                         c_int, c_void_p])
+    act = torch.empty(pairs, inner, dtype=h.dtype, device=device)
+    _check(product(_ptr(h), _ptr(source), _ptr(gate_up), _ptr(act), _ptr(tiles), _ptr(tile_count), max_tiles, inner,
+                   hidden, 1, _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
+    out = torch.empty(pairs, hidden, dtype=h.dtype, device=device)
+    _check(product(_ptr(act), None, _ptr(down), _ptr(out), _ptr(tiles), _ptr(tile_count), max_tiles, hidden, inner, 0,
+                   _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
+    y = torch.empty_like(h)
+    fn = _function("moe", "omnia_moe_combine",
+                   [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(out), _ptr(h), _ptr(place), _ptr(weight), _ptr(y), rows, hidden, top, _code(h.dtype), _stream()),
+           "moe_combine")
+    return y
+
+
+class _NoStep:
+    """Stands in for a step where an op is called on its own (tests of single kernels)."""
+    workspace = None

@@ -194,3 +194,103 @@ class LatentAttention(Mixer):
         out = torch.empty(tokens, H, self.vdim, dtype=proj.dtype, device=proj.device)
         ops.batched_mm(o_lat, self.uv_t, out=out.transpose(0, 1))
         return ops.linear(out.view(tokens, H * self.vdim), self.o)
+
+
+@register_mixer("sink_window_attention")
+class SinkWindowAttention(Mixer):
+    """Grouped-query causal attention with the options a sliding-window design with a softmax sink
+    needs, each a parameter:
+
+    hidden, heads, kv_heads: sizes; dim: width of a query/key head; vdim: width of a value head
+    scale:      multiplies q.k
+    window:     None, or how many latest positions (the query's own included) are visible;
+    keep_first: with a window, how many of the request's first positions stay visible behind it
+                (they keep their own positions for the rotation)
+    norm_eps:   None, or the eps of an RMS norm of every q and k head, with a weight of the head's size
+                shared by the heads (tensors `q.norm`, `k.norm`), applied before the rotation
+    position:   PartSpec of a half-split rotary encoding over the first `dims` <= dim of a head
+    bias:       q, k and v projections have biases (`q.b`, `k.b`, `v.b`), added before the norm
+    sink:       the softmax's denominator also holds exp(sink_h), one learned number a head (`sink`),
+                unscaled, with no key and no value
+    own_kv:     False for a layer without k/v tensors that reads another layer's cache (as that cache
+                holds the keys: normed and rotated) with queries, window and sink of its own
+
+    Tensors: `q` [heads * dim, hidden], `k` [kv_heads * dim, hidden], `v` [kv_heads * vdim, hidden],
+    `o` [hidden, heads * vdim]."""
+
+    graph_safe = True
+    graph_safe_mixed = True
+
+    def __init__(self, hidden: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
+                 window: int | None = None, keep_first: int = 0, norm_eps: float | None = None,
+                 position: PartSpec | None = None, bias: bool = False, sink: bool = False, own_kv: bool = True) -> None:
+        if heads % kv_heads:
+            raise ValueError(f"{heads} query heads do not divide into {kv_heads} groups")
+        if dim > 256 or vdim > 256:
+            raise ValueError(f"head widths of at most 256, got {dim} and {vdim}")
+        if keep_first and window is None:
+            keep_first = 0  # everything is visible anyway
+        self.hidden, self.heads, self.kv_heads, self.dim, self.vdim = hidden, heads, kv_heads, dim, vdim
+        self.scale, self.window, self.keep_first, self.norm_eps = float(scale), window, int(keep_first), norm_eps
+        self.bias, self.sink, self.own_kv = bias, sink, own_kv
+        self.position = POSITIONS.build(position or PartSpec("none"))
+        if getattr(self.position, "pairing", "half") != "half":
+            raise ValueError("sink_window_attention rotates half-split pairs")
+        if getattr(self.position, "dims", 0) > dim:
+            raise ValueError(f"{self.position.dims} rotary dims do not fit a head of {dim}")
+
+    def kv_spec(self) -> KVSpec:
+        return KVSpec(((self.kv_heads, self.dim), (self.kv_heads, self.vdim)), self.window, keep_first=self.keep_first)
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        H, G, dk, dv = self.heads, self.kv_heads, self.dim, self.vdim
+        specs = {"q": TensorSpec((H * dk, self.hidden)), "o": TensorSpec((self.hidden, H * dv))}
+        if self.bias:
+            specs["q.b"] = TensorSpec((H * dk,))
+        if self.norm_eps is not None:
+            specs["q.norm"] = TensorSpec((dk,), "vector")
+        if self.sink:
+            specs["sink"] = TensorSpec((H,), "vector")
+        if self.own_kv:
+            specs["k"], specs["v"] = TensorSpec((G * dk, self.hidden)), TensorSpec((G * dv, self.hidden))
+            if self.bias:
+                specs["k.b"], specs["v.b"] = TensorSpec((G * dk,)), TensorSpec((G * dv,))
+            if self.norm_eps is not None:
+                specs["k.norm"] = TensorSpec((dk,), "vector")
+        return specs
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        self.position.load({}, runtime)
+        names = ["q", "k", "v"] if self.own_kv else ["q"]
+        rows = [tensors[name] for name in names]
+        self.k_col = self.heads * self.dim
+        self.v_col = self.k_col + self.kv_heads * self.dim
+        total = sum(r.shape[0] for r in rows)
+        pad = -total % 8  # rows of the operand in steps of 8, for the kernels that want them so
+        if pad:
+            rows.append(torch.zeros(pad, self.hidden, dtype=rows[0].dtype, device=rows[0].device))
+        self.in_proj = torch.cat(rows, dim=0).contiguous()
+        self.in_bias = None
+        if self.bias:
+            parts = [tensors[name + ".b"] for name in names]
+            if pad:
+                parts.append(torch.zeros(pad, dtype=parts[0].dtype, device=parts[0].device))
+            self.in_bias = torch.cat(parts).contiguous()
+        self.q_norm = tensors["q.norm"].contiguous() if self.norm_eps is not None else None
+        self.k_norm = tensors["k.norm"].contiguous() if self.norm_eps is not None and self.own_kv else None
+        self.sink_logits = tensors["sink"].contiguous() if self.sink else None
+        self.o = tensors["o"].contiguous()
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        if ctx.kv is None:
+            raise RuntimeError("an attention mixer needs cache pages")
+        if ctx.kv.writes and not self.own_kv:
+            raise RuntimeError("a mixer without k/v projections cannot own a cache entry")
+        proj = ops.linear(h, self.in_proj)
+        q = ops.qkv_prepare(proj, 0, self.k_col, self.v_col, self.heads, self.dim, self.in_bias, self.q_norm,
+                            self.k_norm, self.norm_eps, self.position.table(), ctx.step.positions, ctx.kv,
+                            store=self.own_kv)
+        out = ops.paged_attention(q, ctx.kv, ctx.step, self.scale, sink=self.sink_logits, window=self.window,
+                                  keep_first=self.keep_first)
+        return ops.linear(out, self.o)

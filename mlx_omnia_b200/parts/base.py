@@ -28,7 +28,8 @@ FeedForward:  ``forward(h, ctx) -> branch``
 Norm:         ``forward(x) -> h`` and the attributes ``weight``, ``eps`` that the
               fused residual kernel reads (``weight is None`` means weightless)
 Position:     ``table() -> float32[rotary_dims / 2] | None`` of inverse frequencies
-Embedding:    ``forward(token_ids, positions) -> x`` float32 [tokens, hidden]
+Embedding:    ``forward(token_ids, positions) -> x`` float32 [tokens, hidden]; ``state_spec()`` may give
+              named per-request state (the token before, say), found in ``step.model_state``
 Block:        ``entry_norm`` and ``forward(x, h, ctx, exit_norm) -> (x, h_next)``; a block whose
               ``entry_norm`` is None does its own entry from the residual it is handed (`h` is then
               None, and the block before it is given no exit norm); ``state_spec()`` may give named
@@ -62,6 +63,8 @@ class KVSpec:
              equal ones (its keys and its values), a mixer with a latent cache one, a mixer
              whose keys and values differ in width two unequal ones.
     window:  how many of the latest positions can still be read (None: all of them).
+    keep_first: with a window, how many of a request's first positions stay readable for good
+             (their pages are never given back); 0 without a window.
     stride:  positions per stored row (1: one row for every position; n: one row for every
              n positions, as a mixer that keeps a compressed history would want).
     Layers with equal specs share one group of pages."""
@@ -69,12 +72,15 @@ class KVSpec:
     rows: tuple[tuple[int, int], ...]
     window: int | None = None
     stride: int = 1
+    keep_first: int = 0
 
     def __post_init__(self) -> None:
         if not self.rows or any(h < 1 or w < 1 for h, w in self.rows):
             raise ValueError(f"a cache row needs positive (heads, width) entries, got {self.rows}")
         if self.stride < 1 or (self.window is not None and self.window < 1):
             raise ValueError("stride and window must be at least 1")
+        if self.keep_first < 0 or (self.keep_first and self.window is None):
+            raise ValueError("keep_first is a number of positions (at least 0) kept beside a window")
 
     @classmethod
     def keys_and_values(cls, kv_heads: int, head_dim: int, window: int | None = None) -> "KVSpec":
@@ -168,6 +174,12 @@ class Embedding(Part):
     """Turns the step's tokens into the float32 residual stream. It is told where each
     token stands, so an encoding that is added to the embeddings (learned absolute
     positions, say) is a part like any other."""
+
+    def state_spec(self) -> "dict[str, StateSpec] | None":
+        """Named per-request state of the embedding itself (zeros at a request's start). An embedding
+        that declares some is called as ``forward(token_ids, positions, step)`` and finds its
+        tensors, each `[slots + 1, *shape]`, in ``step.model_state``."""
+        return None
 
     def forward(self, token_ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
@@ -266,6 +278,11 @@ class KVView:
     writes: bool = True
     spec: KVSpec | None = None
 
+    @property
+    def keep_first(self) -> int:
+        """How many first positions stay readable beside the window."""
+        return self.spec.keep_first if self.spec is not None else 0
+
     def row(self, index: int) -> torch.Tensor:
         """Row `index` of every page: [num_pages, heads, page_size, width]."""
         if self.pages.dim() == 5:
@@ -300,6 +317,7 @@ class StepContext:
     decode_only: bool
     groups: dict[int, tuple[torch.Tensor, torch.Tensor]]  # group -> (block_table, slot_mapping)
     workspace: Any = None
+    model_state: "dict[str, torch.Tensor] | None" = None  # the embedding's named per-request state
 
 
 @dataclass

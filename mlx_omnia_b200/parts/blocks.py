@@ -217,3 +217,71 @@ class HyperPreNormBlock(Block):
             return total, out
         total = x.view(x.shape[0], n, self.hidden).sum(1) if n > 1 else x
         return total, exit_norm.forward(total)
+
+
+@register_block("branch_norm")
+class BranchNormBlock(Block):
+    """Norms on the branches' outputs only: x += norm1(mixer(x)), then x += norm2(feed_forward(x)).
+    Both branches read the residual itself (rounded to the engine's dtype), so the block has no entry
+    norm; the rounding of the new residual for whoever reads it next is part of the residual step's
+    one pass over the row. A block of this kind hands that rounded residual on, and takes it from
+    the block before when that one made it.
+
+    mixer:        PartSpec of the mixer; feed_forward: PartSpec or None (one branch only)
+    norms:        {"norm1": spec, "norm2": spec} (norm2 only with a feed-forward)
+    """
+
+    entry_norm = None
+
+    def __init__(self, mixer: PartSpec, feed_forward: PartSpec | None, norms: dict[str, PartSpec],
+                 mixer_name: str = "mix", feed_forward_name: str = "mlp") -> None:
+        self.mixer = MIXERS.build(mixer)
+        self.feed_forward = FEED_FORWARDS.build(feed_forward) if feed_forward is not None else None
+        wanted = ("norm1", "norm2") if feed_forward is not None else ("norm1",)
+        if set(wanted) - set(norms):
+            raise ValueError(f"branch_norm needs the norms {wanted}")
+        self.norms = {name: NORMS.build(norms[name]) for name in wanted}
+        self.mixer_name, self.feed_forward_name = mixer_name, feed_forward_name
+
+    def children(self):
+        yield self.mixer_name, self.mixer
+        if self.feed_forward is not None:
+            yield self.feed_forward_name, self.feed_forward
+        yield from self.norms.items()
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {f"{name}.{local}": spec for name, part in self.children() for local, spec in part.tensors().items()}
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        for name, part in self.children():
+            prefix = name + "."
+            part.load({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, runtime)
+
+    def _step(self, x, branch, norm, exit_norm, last: bool):
+        """x += norm(branch); -> what the next reader wants: the exit norm's output after the block's
+        last branch when one is asked for, else x rounded to the engine's dtype."""
+        rms = isinstance(norm, RMSNorm) and norm.groups == 1
+        if not rms:
+            branch, norm = norm.forward(branch.float()).to(branch.dtype), None
+        weight, eps = (norm.weight, norm.eps) if norm is not None else (None, None)
+        if last and exit_norm is not None:
+            if isinstance(exit_norm, RMSNorm) and exit_norm.groups == 1:
+                return ops.add_rmsnorm(x, branch, weight, eps, exit_norm.weight, exit_norm.eps)
+            ops.add_rmsnorm(x, branch, weight, eps, None, None)
+            return exit_norm.forward(x)
+        if self.runtime.exact:
+            ops.add_rmsnorm(x, branch, weight, eps, None, None)
+            return x
+        return ops.add_rmsnorm(x, branch, weight, eps, None, None, rounded=True)
+
+    def forward(self, x, h, ctx, exit_norm):
+        if h is None:
+            h = ops.rounded_rows(x, self.runtime.dtype)
+        h = ops.settle(h)
+        a = self.mixer.forward(h, ctx)
+        h2 = self._step(x, a, self.norms["norm1"], exit_norm, self.feed_forward is None)
+        if self.feed_forward is None:
+            return x, h2
+        m = self.feed_forward.forward(h2, ctx)
+        return x, self._step(x, m, self.norms["norm2"], exit_norm, True)

@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 
 from mlx_omnia_b200.kernels import ops
-from mlx_omnia_b200.parts.base import Embedding, Part, TensorSpec, register_embedding, register_head
+from mlx_omnia_b200.parts.base import Embedding, Part, StateSpec, TensorSpec, register_embedding, register_head
 
 
 @register_embedding("token_embedding")
@@ -68,3 +68,35 @@ class LMHead(Part):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return ops.linear_softcap(h, self.weight, self.multiplier, self.softcap)
+
+
+@register_embedding("pair_hash_embedding")
+class PairHashEmbedding(Embedding):
+    """x = table[id] * scale + pairs[(id_before * mul_prev + id * mul_cur) mod buckets]: beside its own
+    row a token gets a row that its pair with the token before it is hashed to. `pairs` has
+    buckets + 1 rows; the extra last row is the one of a request's first token. The token before a
+    portion's first token is per-request state (`prev`, one int32 a slot). float32 out.
+
+    Tensors: `weight` [vocab, hidden], `pairs` [buckets + 1, hidden]."""
+
+    def __init__(self, vocab: int, hidden: int, buckets: int, mul_prev: int, mul_cur: int, scale: float = 1.0) -> None:
+        if buckets < 1 or mul_prev < 0 or mul_cur < 0:
+            raise ValueError(f"pair_hash_embedding: {buckets} buckets, multipliers {mul_prev} and {mul_cur}")
+        self.vocab, self.hidden, self.buckets = vocab, hidden, buckets
+        self.mul_prev, self.mul_cur, self.scale = int(mul_prev), int(mul_cur), float(scale)
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {"weight": TensorSpec((self.vocab, self.hidden)), "pairs": TensorSpec((self.buckets + 1, self.hidden))}
+
+    def state_spec(self):
+        return {"prev": StateSpec((), torch.int32)}
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        self.weight, self.pairs = tensors["weight"].contiguous(), tensors["pairs"].contiguous()
+
+    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor, step=None) -> torch.Tensor:
+        if step is None or not step.model_state:
+            raise RuntimeError("pair_hash_embedding needs the step and its per-request state")
+        return ops.embed_pair(step, self.weight, self.pairs, step.model_state["prev"], self.scale, self.mul_prev,
+                              self.mul_cur)

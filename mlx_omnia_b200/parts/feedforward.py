@@ -63,3 +63,74 @@ class DenseMLP(FeedForward):
 
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         return ops.linear(ops.linear_act(h, self.up, self.activation), self.down)
+
+
+@register_feed_forward("clamped_glu_mlp")
+class ClampedGLUMLP(FeedForward):
+    """down(g * sigmoid(alpha * g) * (u + 1)) with g = min(gate(h), limit) and
+    u = clamp(up(h), -limit, limit); no biases.
+
+    hidden, inner: widths; limit: the clamp; alpha: the sigmoid's slope.
+    Tensors: `gate`, `up` [inner, hidden] (stacked into one operand at load), `down` [hidden, inner].
+    """
+
+    def __init__(self, hidden: int, inner: int, limit: float, alpha: float = 1.702) -> None:
+        if limit <= 0:
+            raise ValueError(f"clamped_glu_mlp needs a positive limit, got {limit}")
+        self.hidden, self.inner, self.limit, self.alpha = hidden, inner, float(limit), float(alpha)
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {"gate": TensorSpec((self.inner, self.hidden)), "up": TensorSpec((self.inner, self.hidden)),
+                "down": TensorSpec((self.hidden, self.inner))}
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        self.gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
+        self.down = tensors["down"].contiguous()
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        return ops.linear(ops.linear_clamped_glu(h, self.gate_up, self.alpha, self.limit), self.down)
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    """A mixture of `experts` small gated feed-forward layers of which every token uses `top`.
+
+    hidden, inner: widths of an expert (down(silu(gate h) * (up h)), no biases)
+    experts:  experts with tensors; identity: router outputs beyond them whose expert hands its
+              input back; top: choices per token
+    The router's logits are taken in float32 (its matrix is kept in float32 whatever the engine's
+    dtype), the scores are a softmax over all experts + identity outputs; the choice is by score +
+    `correction`, the weight is the score itself, not renormalised.
+    Tensors: `router` [experts + identity, hidden], `correction` [experts + identity], and per expert i
+    `e<i>.gate`, `e<i>.up` [inner, hidden], `e<i>.down` [hidden, inner] (stacked at load).
+    """
+
+    def __init__(self, hidden: int, inner: int, experts: int, top: int, identity: int = 0,
+                 correction: bool = True) -> None:
+        if experts < 1 or identity < 0 or not 1 <= top <= experts + identity:
+            raise ValueError(f"routed_experts of {experts} experts and {identity} identity ones, {top} a token")
+        self.hidden, self.inner, self.experts, self.identity, self.top = hidden, inner, experts, identity, top
+        self.corrected = correction
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        outputs = self.experts + self.identity
+        specs = {"router": TensorSpec((outputs, self.hidden), "vector")}
+        if self.corrected:
+            specs["correction"] = TensorSpec((outputs,), "vector")
+        for e in range(self.experts):
+            specs[f"e{e}.gate"] = TensorSpec((self.inner, self.hidden))
+            specs[f"e{e}.up"] = TensorSpec((self.inner, self.hidden))
+            specs[f"e{e}.down"] = TensorSpec((self.hidden, self.inner))
+        return specs
+
+    def load(self, tensors, runtime) -> None:
+        super().load(tensors, runtime)
+        self.router = tensors["router"].contiguous()
+        self.correction = tensors["correction"].contiguous() if self.corrected else None
+        self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
+                                    for e in range(self.experts)]).contiguous()
+        self.down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        return ops.moe_experts(h, self.router, self.correction, self.gate_up, self.down, self.top, ctx.step)

@@ -98,25 +98,43 @@ class DecoderModel:
 
     # -- cache -----------------------------------------------------------------------
     def cache_needs(self) -> list[CacheNeed]:
+        """What every schedule entry asks of the cache manager. An entry that reads another entry's
+        cache keeps rows of the same shapes; its window and kept first positions may be its own, and
+        the owner's pages are then kept for the widest of them."""
+        schedule = self.spec.schedule
+        specs = [self.blocks[entry.layer].mixer.kv_spec() for entry in schedule]
+        owned = list(specs)
+        for e, entry in enumerate(schedule):
+            if entry.reads is None:
+                continue
+            kv, owner = specs[e], owned[entry.reads]
+            if kv is None or owner is None or kv.rows != owner.rows or kv.stride != owner.stride:
+                raise ValueError(f"a schedule entry reads a cache of {specs[entry.reads]} but its mixer keeps {kv}")
+            window = None if kv.window is None or owner.window is None else max(kv.window, owner.window)
+            owned[entry.reads] = KVSpec(owner.rows, window, owner.stride,
+                                        max(kv.keep_first, owner.keep_first) if window is not None else 0)
         needs = []
-        for entry in self.spec.schedule:
+        for e, entry in enumerate(schedule):
             mixer = self.blocks[entry.layer].mixer
-            kv, state = mixer.kv_spec(), mixer.state_spec()
-            if entry.reads is not None:
-                owner = self.blocks[self.spec.schedule[entry.reads].layer].mixer.kv_spec()
-                if kv != owner:
-                    raise ValueError(f"a schedule entry reads a cache of {owner} but its mixer keeps {kv}")
-                kv = None
-            needs.append(CacheNeed(kv, state, entry.reads, mixer.initial_state() if state is not None else None,
+            state = mixer.state_spec()
+            needs.append(CacheNeed(None if entry.reads is not None else owned[e], state, entry.reads,
+                                   mixer.initial_state() if state is not None else None,
                                    self.blocks[entry.layer].state_spec()))
         return needs
+
+    def model_state(self) -> "dict[str, StateSpec] | None":
+        """Per-request state that belongs to no schedule entry (the embedding's)."""
+        return self.embedding.state_spec()
 
     # -- the step --------------------------------------------------------------------
     def forward(self, step: StepContext, layers: list[LayerContext]) -> torch.Tensor:
         """Run this step's tokens through the schedule. -> float32 logits [wanted, vocab]"""
         schedule = self.spec.schedule
         ops.begin_pass(step)
-        x = self.embedding.forward(step.token_ids, step.positions)
+        if self.embedding.state_spec() is not None:
+            x = self.embedding.forward(step.token_ids, step.positions, step)
+        else:
+            x = self.embedding.forward(step.token_ids, step.positions)
         first = self.blocks[schedule[0].layer].entry_norm
         h = first.forward(x) if first is not None else None  # None: the block does its own entry
         for e, entry in enumerate(schedule):
