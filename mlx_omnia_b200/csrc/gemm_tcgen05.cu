@@ -259,7 +259,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // Both halves are rounded to bfloat16 first, as a separate product would round them.
                 const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gate[j + e])));
                 const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[j + e])));
-                v[e] = __fdividef(g, 1.f + __expf(-g)) * u;
+                // cap > 0: the clamped unit (gate below cap, up within +-cap and moved by one, slope `multiplier`).
+                const float gc = cap > 0.f ? fminf(g, cap) : g;
+                const float uc = cap > 0.f ? fminf(fmaxf(u, -cap), cap) + 1.f : u;
+                v[e] = __fdividef(gc, 1.f + __expf(-multiplier * gc)) * uc;
               }
               const int col = n0 + c + j;
               if (col + 1 < pair_offset && (pair_offset & 1) == 0) {
@@ -385,7 +388,7 @@ int launch(const void* a, const void* w, void* out, int m, int n, int k, int pai
 }  // namespace
 
 // epilogue: 0 store bfloat16 [m, n]; 1 SwiGLU, w = [gate rows | up rows] with n = 2 * inner,
-// out bfloat16 [m, inner]; 2 soft cap, out float32 [m, n]. a and w must be 16-byte aligned and
+// out bfloat16 [m, inner] (cap > 0: the clamped unit, the sigmoid's slope in `multiplier`); 2 soft cap, out float32 [m, n]. a and w must be 16-byte aligned and
 // k a multiple of 8 (rows of both matrices start on 16 bytes).
 extern "C" int omnia_gemm_tcgen05(const void* a, const void* w, void* out, int m, int n, int k, int epilogue,
                                   float multiplier, float cap, int* err, cudaStream_t stream) {
@@ -393,7 +396,8 @@ extern "C" int omnia_gemm_tcgen05(const void* a, const void* w, void* out, int m
   if (k <= 0 || k % 8 != 0 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
   if (epilogue == EPI_SWIGLU) {
     if (n % 2) return (int)cudaErrorInvalidValue;
-    return launch<256, 4, EPI_SWIGLU>(a, w, out, m, n, k, n / 2, 1.f, 0.f, err, stream);
+    if (cap < 0.f) return (int)cudaErrorInvalidValue;
+    return launch<256, 4, EPI_SWIGLU>(a, w, out, m, n, k, n / 2, cap > 0.f ? multiplier : 1.f, cap, err, stream);
   }
   if (epilogue == EPI_SOFTCAP) return launch<256, 4, EPI_SOFTCAP>(a, w, out, m, n, k, 0, multiplier, cap, err, stream);
   if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;

@@ -995,12 +995,18 @@ def linear_swiglu(a, gate_up: torch.Tensor) -> torch.Tensor:
 
 def linear_clamped_glu(a: torch.Tensor, gate_up: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
     """g = min(a @ gate^T, limit), u = clamp(a @ up^T, -limit, limit); g sigmoid(alpha g) (u + 1), with
-    gate_up = [gate rows | up rows] -> [rows, inner]."""
+    gate_up = [gate rows | up rows] -> [rows, inner]. The unit sits in the product's epilogue where
+    SwiGLU does: the weight-streaming kernel up to 16 rows, the tcgen05 kernels from FUSED_GATE_ROWS
+    on; in between, and on the 32-bit path, the library's product and the unit's own kernel."""
+    if limit <= 0:
+        raise KernelError(f"the clamped gated unit needs a positive limit, got {limit}")
     if _skinny(a, gate_up):
-        gu = _gemv_stream(a, gate_up, torch.empty(a.shape[0], gate_up.shape[0], dtype=a.dtype, device=a.device), 0)
-    else:
-        gu = _library_mm(a, gate_up)
-    return clamped_glu(gu, alpha, limit)
+        out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
+        return _gemv_stream(a, gate_up, out, 1, alpha, limit)
+    if _tensor_core(a, gate_up, FUSED_GATE_ROWS):
+        out = torch.empty(a.shape[0], gate_up.shape[0] // 2, dtype=a.dtype, device=a.device)
+        return _gemm_tcgen05(a, gate_up, out, 1, alpha, limit)
+    return clamped_glu(_library_mm(a, gate_up), alpha, limit)
 
 
 def linear_softcap(a: torch.Tensor, weight: torch.Tensor, multiplier: float, cap: float | None) -> torch.Tensor:
