@@ -21,7 +21,10 @@ attention (TFLOP/s). Data is synthetic: seeded uniform-random token ids.
 `--only fokalorn` is a record of its own: prefill and decode throughput of the Fokalorn design at a
 few sizes that resemble a real model's layers (random weights), beside Muse-Glimmer at equal width,
 depth, heads and feed-forward, and each kernel of the new design alone against its roofline beside
-the like kernel of Muse-Glimmer (`--size` picks one size).
+the like kernel of Muse-Glimmer (`--size` picks one size). `--only dolutar` is the same kind of record for
+the Dolutar design (sliding-window attention with kept first positions and a sink, a clamped gated unit,
+routed experts), beside Muse-Glimmer with sliding attention at equal width, depth, heads, window and
+active feed-forward width.
 """
 
 from __future__ import annotations
@@ -775,6 +778,235 @@ def run_fokalorn(args) -> dict:
     return record
 
 
+DOLUTAR_SIZES = {
+    # width, heads x head size, key/value heads, layers, window and kept positions, the dense layer's
+    # feed-forward, experts (with tensors + identity) of which `top` a token, an expert's feed-forward
+    "1024": dict(width=1024, heads=16, dim=64, kv=4, layers=8, window=512, keep=64, ff=4096, experts=16, identity=2, top=2, eff=1024),
+    "2048": dict(width=2048, heads=16, dim=128, kv=4, layers=8, window=512, keep=64, ff=8192, experts=32, identity=4, top=4, eff=1536),
+    "4096": dict(width=4096, heads=32, dim=128, kv=8, layers=4, window=1024, keep=128, ff=12288, experts=16, identity=2, top=4, eff=2048),
+}
+DOLUTAR_VOCAB = 32768
+
+
+def dolutar_config(size: dict) -> dict:
+    """The first layer with the dense feed-forward, the others routed; every second layer reads the
+    cache of the layer before it."""
+    layers = []
+    for i in range(size["layers"]):
+        mixer = {"heads": size["heads"], "kv_heads": size["kv"], "dim": size["dim"], "vdim": size["dim"],
+                 "scale": size["dim"] ** -0.5, "rot": {"base": 100000.0, "dims": size["dim"]},
+                 "mask": {"size": size["window"], "keep_first": size["keep"]}}
+        if i % 2 == 1:
+            mixer["kv_from"] = i - 1
+        mlp = {"kind": "dense", "ff": size["ff"], "limit": 7.0} if i == 0 else \
+            {"kind": "moe", "expert": {"ff": size["eff"]},
+             "router": {"experts": size["experts"], "identity": size["identity"], "top": size["top"]}}
+        layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Dolutar", "vocab": DOLUTAR_VOCAB, "width": size["width"], "logit_scale": 1.0,
+            "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+            "layers": layers}
+
+
+def muse_config_like_dolutar(size: dict) -> dict:
+    """Muse-Glimmer with sliding attention at the same width, depth, heads and window; its feed-forward
+    as wide as the experts one token of the routed design uses."""
+    raw = json.loads(json.dumps(CONFIG2))
+    n = size["layers"]
+    raw["text_config"].update(hidden_size=size["width"], intermediate_size=size["top"] * size["eff"], num_hidden_layers=n,
+                              num_attention_heads=size["heads"], num_key_value_heads=size["kv"], head_dim=size["dim"],
+                              vocab_size=DOLUTAR_VOCAB, layer_types=["sliding_attention"] * n, sliding_window=size["window"],
+                              layer_rope_theta=[100000.0] * n, tie_word_embeddings=False)
+    return raw
+
+
+def run_dolutar(args) -> dict:
+    """Prefill (one prompt of --prefill-tokens) and decode (--batch requests ending at --context tokens)
+    of Dolutar and of Muse-Glimmer at equal sizes, then the new design's kernels alone, each beside the
+    like kernel of Muse-Glimmer."""
+    import torch
+
+    from mlx_omnia_b200.engine.engine import Engine, EngineArgs
+    from mlx_omnia_b200.engine.step import StepEntry
+    from mlx_omnia_b200.kernels import ops
+    from mlx_omnia_b200.parts.base import KVSpec, KVView
+
+    measured, peak_source = peaks()
+    hbm, flops_peak = measured["hbm_gbs"] * 1e9, measured["bf16_tflops"] * 1e12
+    g = torch.Generator().manual_seed(SEED)
+    steps, warmup, batch, context, tokens = args.steps, max(args.warmup, 3), args.batch, args.context, args.prefill_tokens
+    dev, bf = torch.device("cuda:0"), torch.bfloat16
+
+    def timed(fn, count, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(count):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / count
+
+    def whole_model(raw) -> dict:
+        engine = Engine.from_random(raw, SEED, EngineArgs(dtype="bfloat16", page_size=16, max_requests=batch + 1,
+                                                          cache_tokens=batch * (context + 16) + tokens + 16))
+        times = []
+        for index in range(warmup + 3):
+            request = engine.cache.open(f"p{index}")
+            ids = torch.randint(0, DOLUTAR_VOCAB, (tokens,), generator=g).tolist()
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.runner.run([StepEntry(request, ids, [tokens - 1])])
+            stop.record()
+            torch.cuda.synchronize()
+            engine.cache.close(request.request_id)
+            times.append(start.elapsed_time(stop))
+        prefill_ms = statistics.median(times[warmup:])
+        requests = [engine.cache.open(f"d{i}") for i in range(batch)]
+        length = context - steps - warmup - 1
+        for r in requests:
+            engine.runner.run([StepEntry(r, torch.randint(0, DOLUTAR_VOCAB, (length,), generator=g).tolist(), [])])
+        entries = lambda i: [StepEntry(r, [1 + i], [0]) for r in requests]
+        for i in range(warmup):
+            engine.runner.run(entries(i), copy=False)
+        torch.cuda.synchronize()
+        launches = ops.launches
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            engine.runner.run(entries(warmup + i), copy=False)
+        stop.record()
+        torch.cuda.synchronize()
+        decode_ms = start.elapsed_time(stop) / steps
+        ops.raise_on_error(engine.runtime.device)
+        out = {"prefill_tokens_per_s": round(tokens * 1000.0 / prefill_ms, 1), "prefill_ms": round(prefill_ms, 3),
+               "decode_tokens_per_s": round(batch * 1000.0 / decode_ms, 1), "decode_ms": round(decode_ms, 4),
+               "launches_per_decode_step": (ops.launches - launches) // steps}
+        for r in requests:
+            engine.cache.close(r.request_id)
+        del engine
+        torch.cuda.empty_cache()
+        return out
+
+    class Step:
+        pass
+
+    def step_of(lens, starts):
+        st = Step()
+        st.num_seqs, st.q_lens = len(lens), list(lens)
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        st.num_tokens = cu[-1]
+        st.cu_seqlens = torch.tensor(cu, dtype=torch.int32, device=dev)
+        st.state_slots = torch.arange(len(lens), dtype=torch.int32, device=dev)
+        st.positions = torch.tensor([s + i for s, n in zip(starts, lens) for i in range(n)], dtype=torch.int32, device=dev)
+        st.seq_lens = torch.tensor([s + n for s, n in zip(starts, lens)], dtype=torch.int32, device=dev)
+        st.seq_lens_host, st.max_q_len = [s + n for s, n in zip(starts, lens)], max(lens)
+        st.max_seq_len = max(st.seq_lens_host)
+        st.decode_only, st.workspace = all(n == 1 for n in lens), None
+        return st
+
+    def kernels(size: dict) -> dict:
+        H, G, d, D = size["heads"], size["kv"], size["dim"], size["width"]
+        window, keep = size["window"], size["keep"]
+        E, R, top, F = size["experts"], size["experts"] + size["identity"], size["top"], size["eff"]
+        out = {}
+
+        def note(name, ms, bytes_=None, flops=None):
+            entry = {"us": round(ms * 1000.0, 2)}
+            if bytes_ is not None:
+                entry.update(gb_s=round(bytes_ / ms / 1e6, 1), frac_hbm=round(bytes_ / (ms / 1e3) / hbm, 4))
+            if flops is not None:
+                entry.update(tflops=round(flops / ms / 1e9, 2), frac_tensor=round(flops / (ms / 1e3) / flops_peak, 4))
+            out[name] = entry
+
+        for mode, lens, starts in (("prefill", [tokens], [0]), ("decode", [1] * batch, [context - 1] * batch)):
+            st = step_of(lens, starts)
+            T = sum(lens)
+            page = 16
+            pages = -(-st.max_seq_len // page)
+            table = torch.arange(len(lens) * pages, dtype=torch.int32, device=dev).view(len(lens), pages)
+            slots = torch.cat([table[i].long()[(st.positions[st.cu_seqlens[i]: st.cu_seqlens[i + 1]] // page).long()] * page
+                               + st.positions[st.cu_seqlens[i]: st.cu_seqlens[i + 1]].long() % page for i in range(len(lens))])
+            cache = (torch.randn(len(lens) * pages, 2, G, page, d, device=dev) * 0.3).to(bf)
+            kv = KVView(cache, table, slots, page, window, True, KVSpec(((G, d), (G, d)), window, keep_first=keep))
+            like_kv = KVView(cache, table, slots, page, window, True, KVSpec.keys_and_values(G, d, window))
+            # the embedding with its pair table, beside the plain lookup
+            st.token_ids = torch.randint(0, DOLUTAR_VOCAB, (T,), device=dev, dtype=torch.int32)
+            emb, pairs = (torch.randn(n, D, device=dev).to(bf) for n in (DOLUTAR_VOCAB, 65522))
+            prev = torch.zeros(len(lens) + 1, dtype=torch.int32, device=dev)
+            note(f"embed_pair_{mode}", timed(lambda: ops.embed_pair(st, emb, pairs, prev, 1.0, 31, 7), 20), bytes_=T * D * (2 + 2 + 4))
+            note(f"like:embed_rmsnorm_{mode}", timed(lambda: ops.embed_rmsnorm(st.token_ids, emb, 1e-6), 20), bytes_=T * D * (2 + 4))
+            # bias, head norms, rotation and the cache write, beside the weightless form
+            cols = (H + 2 * G) * d
+            proj, bias = (torch.randn(T, cols, device=dev) * 0.5).to(bf), torch.randn(cols, device=dev).to(bf)
+            wq = torch.ones(d, device=dev)
+            inv = torch.tensor([100000.0 ** (-2.0 * i / d) for i in range(d // 2)], device=dev)
+            ms = timed(lambda: ops.qkv_prepare(proj, 0, H * d, (H + G) * d, H, d, bias, wq, wq, 1e-5, inv, st.positions, kv, True), 20)
+            note(f"qkv_prepare_{mode}", ms, bytes_=T * cols * 4)
+            ms = timed(lambda: ops.qk_norm_rope_store(proj, 0, H * d, (H + G) * d, H, G, d, 1e-5, inv, st.positions, like_kv), 20)
+            note(f"like:qk_norm_rope_store_{mode}", ms, bytes_=T * cols * 4)
+            # attention: window, kept positions and sink, beside the same window without them
+            q = (torch.randn(T, H, d, device=dev) * 0.3).to(bf)
+            sink = torch.zeros(H, device=dev)
+            seen = sum(min(s + i + 1, window) for s, n in zip(starts, lens) for i in range(n))  # (query, key) pairs in the windows
+            held = sum(min(s + n, window + n - 1) for s, n in zip(starts, lens))  # keys that are read at all
+            reps = 5 if mode == "prefill" else 20
+            ms = timed(lambda: ops.paged_attention(q, kv, st, d ** -0.5, sink=sink, window=window, keep_first=keep), reps, 2)
+            note(f"sink_window_attention_{mode}", ms, bytes_=held * 2 * G * d * 2 + 4 * T * H * d, flops=4 * seen * H * d)
+            ms = timed(lambda: ops.paged_attention(q, like_kv, st, d ** -0.5), reps, 2)
+            note(f"like:paged_attention_{mode}", ms, bytes_=held * 2 * G * d * 2 + 4 * T * H * d, flops=4 * seen * H * d)
+            # the residual step that also rounds the residual for the next reader, beside the one that norms it
+            x1, y = torch.randn(T, D, device=dev), torch.randn(T, D, device=dev).to(bf)
+            w = torch.ones(D, device=dev)
+            note(f"add_norm_rounded_{mode}", timed(lambda: ops.add_rmsnorm(x1, y, w, 1e-5, None, None, rounded=True), 20),
+                 bytes_=T * (2 * D * 4 + 2 * D * 2))
+            note(f"like:add_rmsnorm_{mode}", timed(lambda: ops.add_rmsnorm(x1, y, w, 1e-5, w, 1e-5), 20), bytes_=T * (2 * D * 4 + 2 * D * 2))
+            # the dense layer's clamped unit in its product, beside SwiGLU in the same product
+            h = (torch.randn(T, D, device=dev) * 0.5).to(bf)
+            gate_up = (torch.randn(2 * size["ff"], D, device=dev) * D ** -0.5).to(bf)
+            dense = dict(bytes_=2 * size["ff"] * D * 2 + T * (D + size["ff"]) * 2, flops=2 * T * 2 * size["ff"] * D)
+            note(f"linear_clamped_glu_{mode}", timed(lambda: ops.linear_clamped_glu(h, gate_up, 1.702, 7.0), 10), **dense)
+            note(f"like:linear_swiglu_{mode}", timed(lambda: ops.linear_swiglu(h, gate_up), 10), **dense)
+            del gate_up
+            # routed experts: router, sorted order, the two grouped products, the weighted sum; beside the dense
+            # feed-forward of the same active width (gate|up with SwiGLU, then down)
+            router, correction = torch.randn(R, D, device=dev) * 0.05, torch.zeros(R, device=dev)
+            egu = (torch.randn(E, 2 * F, D, device=dev) * D ** -0.5).to(bf)
+            edn = (torch.randn(E, D, F, device=dev) * F ** -0.5).to(bf)
+            counts = torch.zeros(E, dtype=torch.int32, device=dev)
+
+            def route():
+                counts.zero_()
+                return ops.moe_route(h, router, correction, E, top, counts)
+
+            note(f"moe_route_{mode}", timed(route, 20), bytes_=T * D * 2 + R * D * 4)
+            ms = timed(lambda: ops.moe_experts(h, router, correction, egu, edn, top, st), 10)
+            used = min(E, T * top)  # experts whose weights a step reads at most
+            note(f"moe_experts_{mode}", ms, bytes_=used * 3 * F * D * 2 + T * D * 4, flops=2 * T * top * 3 * F * D)
+            dgu = (torch.randn(2 * top * F, D, device=dev) * D ** -0.5).to(bf)
+            ddn = (torch.randn(D, top * F, device=dev) * (top * F) ** -0.5).to(bf)
+            ms = timed(lambda: ops.linear(ops.linear_swiglu(h, dgu), ddn), 10)
+            note(f"like:gated_mlp_{mode}", ms, bytes_=3 * top * F * D * 2 + T * D * 4, flops=2 * T * top * 3 * F * D)
+            del egu, edn, dgu, ddn
+        ops.raise_on_error(dev)
+        return out
+
+    record = {"metric": "Dolutar beside Muse-Glimmer (sliding attention) at equal sizes", "unit": "tokens/s", "dtype": "bf16",
+              "data": "synthetic: seeded uniform-random token ids, random weights",
+              "config": {"prefill_tokens": tokens, "decode_batch": batch, "decode_context": context, "vocab": DOLUTAR_VOCAB,
+                         "peaks": peak_source}, "sizes": {}}
+    for name in ([args.size] if args.size else list(DOLUTAR_SIZES)):
+        size = DOLUTAR_SIZES[name]
+        record["sizes"][name] = {"dolutar": whole_model(dolutar_config(size)),
+                                 "muse_glimmer": whole_model(muse_config_like_dolutar(size)),
+                                 "kernels": kernels(size), "layers": size["layers"]}
+    return record
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -786,7 +1018,8 @@ def main() -> int:
     parser.add_argument("--timeline", action="store_true",
                         help="with --only decode|prefill and OMNIA_TIMELINE=1 in the environment: one step's "
                              "kernels with the time each takes in the stream, on stderr")
-    parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "portions", "sampling", "products", "elementwise", "fokalorn"], default="all",
+    parser.add_argument("--only", choices=["all", "decode", "prefill", "mixed", "portions", "sampling", "products", "elementwise", "fokalorn",
+                                           "dolutar"], default="all",
                         help="time one part only (small cases for profilers); prints a short record")
     parser.add_argument("--config", type=int, choices=sorted(CONFIGS), default=2,
                         help="with --only: the sizes of another benchmark configuration (3: 36 layers, hidden 4096, "
@@ -798,7 +1031,7 @@ def main() -> int:
     parser.add_argument("--portion", type=int, default=256,
                         help="--only mixed: tokens of a prompt that run beside --batch decoding requests")
     parser.add_argument("--size", choices=sorted(FOKALORN_SIZES), default=None,
-                        help="--only fokalorn: one size instead of all")
+                        help="--only fokalorn or dolutar: one size instead of all")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -814,6 +1047,9 @@ def main() -> int:
     args.context = args.context or CONFIGS[args.config][1]
     if args.only == "fokalorn":
         print(json.dumps(run_fokalorn(args)))
+        return 0
+    if args.only == "dolutar":
+        print(json.dumps(run_dolutar(args)))
         return 0
     if args.only == "all":
         args.warmup = max(args.warmup, 3)

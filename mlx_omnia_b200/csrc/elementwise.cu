@@ -470,69 +470,72 @@ extern "C" int omnia_qk_norm_rope_store(const void* proj, int row_stride, int q_
 // of dims (i, i + rot / 2) by position * inv_freq[i]; q goes to q_out [tokens, nq, dk], k and v to
 // the token's slot of the cache: key row (head h) at k_pages + page * page_stride + (h * page_size
 // + offset) * dk, value row at v_pages + page * page_stride + (h * page_size + offset) * dv.
-// One warp per (token, head).
+// One block per token, its warps taking the heads in turn.
 template <typename T>
-__global__ void qkv_prepare_kernel(const T* __restrict__ proj, int row_stride, int q_col, int k_col, int v_col,
-                                   int nq, int nkv, int dk, int dv, const T* __restrict__ bias,
-                                   const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
-                                   const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
-                                   const long long* __restrict__ slot_mapping, T* __restrict__ q_out,
-                                   T* __restrict__ k_pages, T* __restrict__ v_pages, long long page_stride,
-                                   int page_size, long long num_slots, int* err) {
+__global__ void __launch_bounds__(256)
+qkv_prepare_kernel(const T* __restrict__ proj, int row_stride, int q_col, int k_col, int v_col,
+                   int nq, int nkv, int dk, int dv, const T* __restrict__ bias,
+                   const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                   const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
+                   const long long* __restrict__ slot_mapping, T* __restrict__ q_out,
+                   T* __restrict__ k_pages, T* __restrict__ v_pages, long long page_stride,
+                   int page_size, long long num_slots, int* err) {
   pdl_wait();
   pdl_launch_dependents();
+  // One block per token: the token's angles are worked out once for all its heads.
+  __shared__ float cos_s[128], sin_s[128];
+  __shared__ float staged[8][256];
   const int t = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hs = blockIdx.y * (blockDim.x >> 5) + warp;
-  if (hs >= nq + 2 * nkv) return;
-  const int kind = hs < nq ? 0 : (hs < nq + nkv ? 1 : 2);
-  const int head = kind == 0 ? hs : (kind == 1 ? hs - nq : hs - nq - nkv);
-  const int d = kind == 2 ? dv : dk;
-  const int col = (kind == 0 ? q_col : kind == 1 ? k_col : v_col) + head * d;
-  const T* src = proj + (size_t)t * row_stride + col;
-  const T* b = bias ? bias + col : nullptr;
-  T* dst;
-  if (kind == 0) {
-    dst = q_out + ((size_t)t * nq + head) * dk;
-  } else {
-    const long long slot = slot_mapping[t];
-    if (slot < 0) return;
-    if (slot >= num_slots) {
-      if (lane == 0) atomicOr(err, OMNIA_ERR_SLOT);
-      return;
-    }
-    const long long page = slot / page_size, off = slot % page_size;
-    dst = (kind == 1 ? k_pages : v_pages) + page * page_stride + ((long long)head * page_size + off) * d;
-  }
-  if (kind == 2) {
-    for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(to_f32(src[i]) + (b ? to_f32(b[i]) : 0.f));
-    return;
-  }
-  __shared__ float staged[4][256];
-  float* v = staged[warp];
-  const float* w = kind == 0 ? q_weight : k_weight;
-  float ss = 0.f;
-  for (int i = lane; i < d; i += 32) {
-    const float a = to_f32(src[i]) + (b ? to_f32(b[i]) : 0.f);
-    v[i] = a;
-    ss += a * a;
-  }
-  float scale = 1.f;
-  if (eps >= 0.f) scale = rsqrtf(warp_sum(ss) / (float)d + eps);
-  __syncwarp();
-  if (eps >= 0.f)
-    for (int i = lane; i < d; i += 32) v[i] = v[i] * scale * (w ? w[i] : 1.f);
-  __syncwarp();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int rhalf = inv_freq != nullptr ? rot / 2 : 0;
-  const float pos = (float)positions[t];
-  for (int i = lane; i < rhalf; i += 32) {
-    float s, c;
-    sincosf(pos * inv_freq[i], &s, &c);
-    const float a0 = v[i], a1 = v[i + rhalf];
-    dst[i] = from_f32<T>(a0 * c - a1 * s);
-    dst[i + rhalf] = from_f32<T>(a1 * c + a0 * s);
+  {
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < rhalf; i += blockDim.x) sincosf(pos * inv_freq[i], &sin_s[i], &cos_s[i]);
   }
-  for (int i = 2 * rhalf + lane; i < d; i += 32) dst[i] = from_f32<T>(v[i]);
+  __syncthreads();
+  const long long slot = slot_mapping != nullptr ? slot_mapping[t] : -1;
+  if (nkv > 0 && slot >= num_slots && threadIdx.x == 0) atomicOr(err, OMNIA_ERR_SLOT);
+  float* v = staged[warp];
+  for (int hs = warp; hs < nq + 2 * nkv; hs += warps) {
+    const int kind = hs < nq ? 0 : (hs < nq + nkv ? 1 : 2);
+    const int head = kind == 0 ? hs : (kind == 1 ? hs - nq : hs - nq - nkv);
+    const int d = kind == 2 ? dv : dk;
+    const int col = (kind == 0 ? q_col : kind == 1 ? k_col : v_col) + head * d;
+    const T* src = proj + (size_t)t * row_stride + col;
+    const T* b = bias ? bias + col : nullptr;
+    T* dst;
+    if (kind == 0) {
+      dst = q_out + ((size_t)t * nq + head) * dk;
+    } else {
+      if (slot < 0 || slot >= num_slots) continue;
+      const long long page = slot / page_size, off = slot % page_size;
+      dst = (kind == 1 ? k_pages : v_pages) + page * page_stride + ((long long)head * page_size + off) * d;
+    }
+    if (kind == 2) {
+      for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(to_f32(src[i]) + (b ? to_f32(b[i]) : 0.f));
+      continue;
+    }
+    const float* w = kind == 0 ? q_weight : k_weight;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      const float a = to_f32(src[i]) + (b ? to_f32(b[i]) : 0.f);
+      v[i] = a;
+      ss += a * a;
+    }
+    const float scale = eps >= 0.f ? rsqrtf(warp_sum(ss) / (float)d + eps) : 1.f;
+    __syncwarp();
+    if (eps >= 0.f)
+      for (int i = lane; i < d; i += 32) v[i] = v[i] * scale * (w ? w[i] : 1.f);
+    __syncwarp();
+    for (int i = lane; i < rhalf; i += 32) {
+      const float c = cos_s[i], sn = sin_s[i];
+      const float a0 = v[i], a1 = v[i + rhalf];
+      dst[i] = from_f32<T>(a0 * c - a1 * sn);
+      dst[i + rhalf] = from_f32<T>(a1 * c + a0 * sn);
+    }
+    for (int i = 2 * rhalf + lane; i < d; i += 32) dst[i] = from_f32<T>(v[i]);
+    __syncwarp();  // the staging row is read before the warp's next head overwrites it
+  }
 }
 
 extern "C" int omnia_qkv_prepare(const void* proj, int row_stride, int q_col, int k_col, int v_col, int nq, int nkv,
@@ -544,8 +547,8 @@ extern "C" int omnia_qkv_prepare(const void* proj, int row_stride, int q_col, in
   if (tokens == 0) return 0;
   if (dk > 256 || dv > 256 || rot > dk || (rot & 1)) return (int)cudaErrorInvalidValue;
   const int heads = nq + 2 * nkv;
-  dim3 grid(tokens, (heads + 3) / 4);
-  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(qkv_prepare_kernel<T>, grid, 128, 0, stream, (const T*)proj, row_stride, q_col,
+  const int threads = heads >= 8 ? 256 : heads >= 4 ? 128 : 64;
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(qkv_prepare_kernel<T>, tokens, threads, 0, stream, (const T*)proj, row_stride, q_col,
                                           k_col, v_col, nq, nkv, dk, dv, (const T*)bias, q_weight, k_weight, eps,
                                           inv_freq, rot, positions, slot_mapping, (T*)q_out, (T*)k_pages, (T*)v_pages,
                                           page_stride, page_size, num_slots, err)));

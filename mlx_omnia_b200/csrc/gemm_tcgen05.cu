@@ -18,6 +18,13 @@
 // Epilogues: 0 store bfloat16; 1 SwiGLU: the B tile holds 128 gate rows and the matching
 // 128 up rows of w, the block stores silu(gate) * up (BLOCK_N 256 only); 2 soft cap to float32.
 //
+// Grouped form (routed experts): the rows of `a` are sorted by expert, w holds every expert's matrix one
+// after the other, and a list made on the device says which runs of at most 128 rows belong to which
+// expert: a row tile is then (expert, first row, rows) from that list instead of a multiple of 128, its
+// weight rows start at expert * rows-per-expert, and the epilogue stores only the tile's own rows (the
+// TMA box of `a` reaches into the next expert's rows, whose products are dropped). How many row tiles
+// there are is read from device memory, so the host never learns where the tokens went.
+//
 // Every wait on a barrier is bounded: when the bound is hit the block raises OMNIA_ERR_TIMEOUT
 // in the error word, every role leaves its loop, the block waits (bounded again) for the TMA
 // loads it still has in flight, frees its tensor memory and returns.
@@ -123,7 +130,8 @@ template <int BLOCK_N, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     void* __restrict__ out, int m, int n, int k, int pair_offset, float multiplier,
-                    float cap, int m_tiles, int n_tiles, int* err) {
+                    float cap, int m_tiles, int n_tiles, const int* __restrict__ group_tiles,
+                    const int* __restrict__ group_count, int group_rows, int* err) {
   constexpr uint32_t A_BYTES = BLOCK_M * BLOCK_K * sizeof(bf16);
   constexpr uint32_t B_BYTES = BLOCK_N * BLOCK_K * sizeof(bf16);
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -137,7 +145,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_blocks = (k + BLOCK_K - 1) / BLOCK_K;
-  const int total_tiles = m_tiles * n_tiles;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
   const uint32_t acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
 
@@ -166,6 +173,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // (the launch is a programmatic dependent launch); from here on its results are read.
   pdl_wait();
   pdl_launch_dependents();
+  // Grouped: the list's length is what the kernel before this one wrote; m_tiles is then its capacity.
+  if (group_tiles != nullptr) m_tiles = min(*group_count, m_tiles);
+  const int total_tiles = m_tiles * n_tiles;
+  // Row tile `mt`: its first row, how many of its 128 rows are its own, and where its weight rows begin.
+  auto row_tile = [&](int mt, int& m0, int& rows, int& w0) {
+    if (group_tiles != nullptr) {
+      w0 = group_tiles[3 * mt] * group_rows, m0 = group_tiles[3 * mt + 1], rows = group_tiles[3 * mt + 2];
+    } else {
+      w0 = 0, m0 = mt * BLOCK_M, rows = BLOCK_M;
+    }
+  };
 
   // Tiles are dealt round-robin; consecutive tiles share the same columns of the output (the
   // same rows of w), so blocks running side by side read the same weight tile out of L2.
@@ -175,7 +193,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * BLOCK_M, n0 = (tile / m_tiles) * TILE_COLS;
+        int m0, tile_rows, w0;
+        row_tile(tile % m_tiles, m0, tile_rows, w0);
+        const int n0 = (tile / m_tiles) * TILE_COLS;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag);
@@ -184,10 +204,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
           tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * BLOCK_K, m0);
           if (EPI == EPI_SWIGLU) {
-            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BLOCK_K, n0);
-            tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * BLOCK_K, pair_offset + n0);
+            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BLOCK_K, w0 + n0);
+            tma_load_2d(b_dst + B_BYTES / 2, &map_b, full0 + 8 * s, kb * BLOCK_K, w0 + pair_offset + n0);
           } else {
-            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BLOCK_K, n0);
+            tma_load_2d(b_dst, &map_b, full0 + 8 * s, kb * BLOCK_K, w0 + n0);
           }
         }
       }
@@ -235,8 +255,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
-      const int m0 = (tile % m_tiles) * BLOCK_M, n0 = (tile / m_tiles) * TILE_COLS;
-      const int row = m0 + quarter * 32 + lane;
+      int m0, tile_rows, w0;
+      row_tile(tile % m_tiles, m0, tile_rows, w0);
+      const int n0 = (tile / m_tiles) * TILE_COLS;
+      const int row = quarter * 32 + lane < tile_rows ? m0 + quarter * 32 + lane : m;  // m: not one of the tile's own
       const uint32_t buf = local & 1;
       ok = mbar_wait(acc_full0 + 8 * buf, (local >> 1) & 1, abort_flag);
       if (!ok) break;
@@ -381,7 +403,34 @@ int launch(const void* a, const void* w, void* out, int m, int n, int k, int pai
   const long long total = (long long)n_tiles * m_tiles;
   const int grid = (int)(total < sm_count ? total : sm_count);  // one persistent block per SM
   launch_pdl(gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI>, grid, THREADS, smem, stream,
-             map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, m_tiles, n_tiles, err);
+             map_a, map_b, out, m, n, k, pair_offset, multiplier, cap, m_tiles, n_tiles, (const int*)nullptr,
+             (const int*)nullptr, 0, err);
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// The grouped form: a [m, k] sorted by expert, w [experts * n, k], tiles [max_tiles, 3] and tile_count on the device.
+template <int BLOCK_N, int STAGES, int EPI>
+int launch_grouped(const void* a, const void* w, void* out, int m, int n, int k, int experts, int pair_offset,
+                   const int* tiles, const int* tile_count, int max_tiles, int* err, cudaStream_t stream) {
+  CUtensorMap map_a, map_b;
+  const int b_box = EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+  if (!make_map(&map_a, a, m, k, BLOCK_M) || !make_map(&map_b, w, experts * n, k, b_box)) return (int)cudaErrorInvalidValue;
+  constexpr size_t smem = (size_t)STAGES * (BLOCK_M + BLOCK_N) * BLOCK_K * sizeof(bf16) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int cols = EPI == EPI_SWIGLU ? pair_offset : n;
+  const int tile_cols = EPI == EPI_SWIGLU ? BLOCK_N / 2 : BLOCK_N;
+  const int n_tiles = (cols + tile_cols - 1) / tile_cols;
+  const int sm_count = omnia_sm_count();
+  const long long total = (long long)n_tiles * max_tiles;
+  const int grid = (int)(total < sm_count ? total : sm_count);
+  launch_pdl(gemm_tcgen05_kernel<BLOCK_N, STAGES, EPI>, grid, THREADS, smem, stream,
+             map_a, map_b, out, m, n, k, pair_offset, 1.f, 0.f, max_tiles, n_tiles, tiles, tile_count, n, err);
   return OMNIA_LAUNCH_RESULT();
 }
 
@@ -409,3 +458,20 @@ extern "C" int omnia_gemm_tcgen05(const void* a, const void* w, void* out, int m
   if (wide_rounds * 100 <= narrow_rounds * 65) return launch<256, 4, EPI_STORE>(a, w, out, m, n, k, 0, 1.f, 0.f, err, stream);
   return launch<128, 6, EPI_STORE>(a, w, out, m, n, k, 0, 1.f, 0.f, err, stream);
 }
+
+// The grouped product of routed experts: a [m, k] rows sorted by expert; w [experts, n, k]; tiles
+// [max_tiles, 3] = (expert, first row, rows <= 128) and tile_count [1] in device memory. epilogue 0:
+// out [m, n] = a w_e^T; 1: n = 2 * inner (gate rows, then up rows), out [m, inner] = silu(gate) * up.
+extern "C" int omnia_gemm_tcgen05_grouped(const void* a, const void* w, void* out, int m, int n, int k, int experts,
+                                          int epilogue, const int* tiles, const int* tile_count, int max_tiles,
+                                          int* err, cudaStream_t stream) {
+  if (m == 0 || n == 0 || max_tiles == 0) return 0;
+  if (k <= 0 || k % 8 != 0 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || experts < 1) return (int)cudaErrorInvalidValue;
+  if (epilogue == EPI_SWIGLU) {
+    if (n % 2) return (int)cudaErrorInvalidValue;
+    return launch_grouped<256, 4, EPI_SWIGLU>(a, w, out, m, n, k, experts, n / 2, tiles, tile_count, max_tiles, err, stream);
+  }
+  if (epilogue != EPI_STORE) return (int)cudaErrorInvalidValue;
+  return launch_grouped<256, 4, EPI_STORE>(a, w, out, m, n, k, experts, 0, tiles, tile_count, max_tiles, err, stream);
+}
+

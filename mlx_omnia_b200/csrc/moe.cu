@@ -21,31 +21,88 @@
 
 namespace {
 
-constexpr int ROUTE_THREADS = 128;
+constexpr int ROUTE_THREADS = 256;
 constexpr int TILE_ROWS = 64;  // rows of a tile of the grouped products
 
 // ---------------------------------------------------------------------------------
-template <typename T>
+// A block routes TOK consecutive tokens (8 where there are many: every router row is then fetched
+// once for eight tokens instead of once a token; 1 in a small step, which wants blocks, not reuse).
+// The tokens' rows wait in shared memory as float32; a warp owns every eighth router output and takes
+// the dot products of four of them with all TOK rows in one pass over the columns.
+// Then warp t finishes token t: softmax over all outputs, choice scores, the `top` largest.
+template <typename T, int TOK>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
-                 int outputs, int experts, int hidden, int top, int* __restrict__ choice,
+                 int tokens, int outputs, int experts, int hidden, int top, int* __restrict__ choice,
                  float* __restrict__ weight, int* __restrict__ counts) {
   pdl_wait();
   pdl_launch_dependents();
-  extern __shared__ float route_s[];  // [outputs] scores, [outputs] choice scores
-  float* score = route_s;
-  float* pick = route_s + outputs;
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const T* row = h + (size_t)t * hidden;
-  for (int e = warp; e < outputs; e += ROUTE_THREADS / 32) {
-    const float* w = router + (size_t)e * hidden;
-    float dot = 0.f;
-    for (int i = lane; i < hidden; i += 32) dot += to_f32(row[i]) * w[i];
-    dot = warp_sum(dot);
-    if (lane == 0) score[e] = dot;
+  constexpr int WARPS = ROUTE_THREADS / 32;
+  static_assert(TOK <= WARPS, "a warp finishes a token");
+  extern __shared__ __align__(16) float route_s[];
+  const int padded = (outputs + 3) / 4 * 4;
+  float* hrow = route_s;                           // [TOK][hidden]
+  float* scores = hrow + (size_t)TOK * hidden;     // [TOK][padded] logits, then scores; [TOK][padded] choice scores
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = blockIdx.x * TOK, live = min(TOK, tokens - t0);
+  for (int tok = 0; tok < TOK; ++tok)
+    for (int i = threadIdx.x; i < hidden; i += ROUTE_THREADS)
+      hrow[(size_t)tok * hidden + i] = tok < live ? to_f32(h[(size_t)(t0 + tok) * hidden + i]) : 0.f;
+  __syncthreads();
+  // Four router outputs a warp at a time (outputs warp, warp + 8, ...): a lane reads a float4 of each
+  // token's row once and uses it against all four, and the four loads of the router's rows, times
+  // the unrolling, are in flight together.
+  constexpr int CHUNK = 4;
+  const bool wide = (hidden & 3) == 0 && ((uintptr_t)router & 15) == 0;
+  for (int e0 = warp; e0 < outputs; e0 += WARPS * CHUNK) {
+    float acc[CHUNK][TOK];
+#pragma unroll
+    for (int c = 0; c < CHUNK; ++c)
+#pragma unroll
+      for (int tok = 0; tok < TOK; ++tok) acc[c][tok] = 0.f;
+    if (wide) {
+      const int quads = hidden / 4;
+      const float4* w4 = reinterpret_cast<const float4*>(router);
+      const float4* h4 = reinterpret_cast<const float4*>(hrow);
+#pragma unroll 2
+      for (int q = lane; q < quads; q += 32) {
+        float4 b[CHUNK];
+#pragma unroll
+        for (int c = 0; c < CHUNK; ++c) {
+          const int e = e0 + c * WARPS;
+          b[c] = e < outputs ? __ldg(w4 + (size_t)e * quads + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int tok = 0; tok < TOK; ++tok) {
+          const float4 a = h4[(size_t)tok * quads + q];
+#pragma unroll
+          for (int c = 0; c < CHUNK; ++c) acc[c][tok] += a.x * b[c].x + a.y * b[c].y + a.z * b[c].z + a.w * b[c].w;
+        }
+      }
+    } else {
+      for (int i = lane; i < hidden; i += 32)
+#pragma unroll
+        for (int c = 0; c < CHUNK; ++c) {
+          const int e = e0 + c * WARPS;
+          const float b = e < outputs ? router[(size_t)e * hidden + i] : 0.f;
+#pragma unroll
+          for (int tok = 0; tok < TOK; ++tok) acc[c][tok] += hrow[(size_t)tok * hidden + i] * b;
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < CHUNK; ++c)
+#pragma unroll
+      for (int tok = 0; tok < TOK; ++tok) {
+        const float v = warp_sum(acc[c][tok]);
+        const int e = e0 + c * WARPS;
+        if (lane == 0 && e < outputs) scores[(size_t)tok * padded + e] = v;
+      }
   }
   __syncthreads();
-  if (warp != 0) return;
+  if (warp >= live) return;
+  const int t = t0 + warp;
+  float* score = scores + (size_t)warp * padded;
+  float* pick = scores + (size_t)(TOK + warp) * padded;
   float top_z = -INFINITY;
   for (int e = lane; e < outputs; e += 32) top_z = fmaxf(top_z, score[e]);
   top_z = warp_max(top_z);
@@ -91,7 +148,8 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
 // offsets [experts + 1]; tiles [max_tiles, 3] = (expert, first row, rows); tile_count [1];
 // counts and cursors are left zero for the launches that follow.
 __global__ void moe_plan_kernel(int* __restrict__ counts, int* __restrict__ cursors, int* __restrict__ offsets,
-                                int* __restrict__ tiles, int* __restrict__ tile_count, int experts, int max_tiles) {
+                                int* __restrict__ tiles, int* __restrict__ tile_count, int experts, int max_tiles,
+                                int tile_rows) {
   pdl_wait();
   pdl_launch_dependents();
   extern __shared__ int plan_s[];  // [experts + 1] row offsets, [experts + 1] tile offsets
@@ -102,7 +160,7 @@ __global__ void moe_plan_kernel(int* __restrict__ counts, int* __restrict__ curs
     for (int e = 0; e < experts; ++e) {
       row0[e] = rows, tile0[e] = listed;
       rows += counts[e];
-      listed += (counts[e] + TILE_ROWS - 1) / TILE_ROWS;
+      listed += (counts[e] + tile_rows - 1) / tile_rows;
     }
     row0[experts] = rows, tile0[experts] = listed;
     *tile_count = min(listed, max_tiles);
@@ -111,10 +169,10 @@ __global__ void moe_plan_kernel(int* __restrict__ counts, int* __restrict__ curs
   for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = row0[e];
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     const int rows = row0[e + 1] - row0[e];
-    for (int i = 0, at = tile0[e]; i * TILE_ROWS < rows && at < max_tiles; ++i, ++at) {
+    for (int i = 0, at = tile0[e]; i * tile_rows < rows && at < max_tiles; ++i, ++at) {
       tiles[3 * at] = e;
-      tiles[3 * at + 1] = row0[e] + i * TILE_ROWS;
-      tiles[3 * at + 2] = min(TILE_ROWS, rows - i * TILE_ROWS);
+      tiles[3 * at + 1] = row0[e] + i * tile_rows;
+      tiles[3 * at + 2] = min(tile_rows, rows - i * tile_rows);
     }
     counts[e] = 0;
     cursors[e] = 0;
@@ -242,6 +300,11 @@ __device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+constexpr int TC_BK = 32, TC_ROW = TC_BK + 8, TC_STAGES = 4;
+constexpr size_t tc_smem_bytes(bool dual) {
+  return (size_t)TC_STAGES * (TILE_ROWS + (dual ? 2 : 1) * 64) * TC_ROW * sizeof(__nv_bfloat16);
+}
+
 template <bool DUAL>
 __global__ void __launch_bounds__(128)
 moe_product_tc_kernel(const bf16* __restrict__ a, const int* __restrict__ source, const bf16* __restrict__ w,
@@ -250,9 +313,12 @@ moe_product_tc_kernel(const bf16* __restrict__ a, const int* __restrict__ source
   pdl_wait();
   pdl_launch_dependents();
   if ((int)blockIdx.x >= *tile_count) return;
-  constexpr int BK = 32, ROW = BK + 8, PARTS = DUAL ? 2 : 1;
-  __shared__ __align__(16) bf16 As[2][TILE_ROWS][ROW];
-  __shared__ __align__(16) bf16 Bs[2][PARTS][64][ROW];
+  constexpr int BK = TC_BK, ROW = TC_ROW, PARTS = DUAL ? 2 : 1, STAGES = TC_STAGES;
+  extern __shared__ __align__(16) unsigned char tc_smem[];
+  typedef bf16 (*ATiles)[TILE_ROWS][ROW];
+  typedef bf16 (*BTiles)[PARTS][64][ROW];
+  ATiles As = reinterpret_cast<ATiles>(tc_smem);                                                  // [STAGES][64][ROW]
+  BTiles Bs = reinterpret_cast<BTiles>(tc_smem + (size_t)STAGES * TILE_ROWS * ROW * sizeof(bf16));  // [STAGES][PARTS][64][ROW]
   __shared__ int src_row[TILE_ROWS];
   const int expert = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1], rows = tiles[3 * blockIdx.x + 2];
   const int n0 = blockIdx.y * 64;
@@ -280,15 +346,22 @@ moe_product_tc_kernel(const bf16* __restrict__ a, const int* __restrict__ source
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[part][j][0] = acc[part][j][1] = acc[part][j][2] = acc[part][j][3] = 0.f;
   const int steps = (k + BK - 1) / BK;
-  load(0, 0);
-  cp_async_commit();
-  const int mat = lane >> 3;
-  for (int step = 0; step < steps; ++step) {
-    if (step + 1 < steps) load((step + 1) * BK, (step + 1) & 1);
+  // A ring of STAGES stages, STAGES - 1 of them on their way at any time: a block with one or two rows
+  // (a decode step) is a stream of weights, and what bounds it is how much of the stream is in flight.
+#pragma unroll
+  for (int s0 = 0; s0 < STAGES - 1; ++s0) {
+    if (s0 < steps) load(s0 * BK, s0);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
-    const int stage = step & 1;
+  }
+  const int mat = lane >> 3;
+  const bool busy = warp * 16 < rows;  // a warp none of whose 16 rows is the tile's own only helps to load
+  for (int step = 0; step < steps; ++step) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();  // stage `step` has landed, and everyone is done with the stage that is filled next
+    if (step + STAGES - 1 < steps) load((step + STAGES - 1) * BK, (step + STAGES - 1) % STAGES);
+    cp_async_commit();
+    const int stage = step % STAGES;
+    if (!busy) continue;
 #pragma unroll
     for (int ks = 0; ks < BK / 16; ++ks) {
       unsigned af[4];
@@ -303,7 +376,6 @@ moe_product_tc_kernel(const bf16* __restrict__ a, const int* __restrict__ source
           mma_bf16(acc[part][2 * j2 + 1], af, b2, b3);
         }
     }
-    __syncthreads();
   }
   cp_async_wait<0>();
   const int g = lane >> 2, t4 = lane & 3;
@@ -345,6 +417,18 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const T* __restri
   }
 }
 
+template <typename T, int TOK>
+int launch_route(const T* h, const float* router, const float* correction, int tokens, int outputs, int experts,
+                 int hidden, int top, int* choice, float* weight, int* counts, size_t smem, cudaStream_t stream) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  launch_pdl(moe_route_kernel<T, TOK>, (tokens + TOK - 1) / TOK, ROUTE_THREADS, smem, stream, h, router, correction, tokens,
+             outputs, experts, hidden, top, choice, weight, counts);
+  return OMNIA_LAUNCH_RESULT();
+}
+
 }  // namespace
 
 extern "C" int omnia_moe_route(const void* h, const float* router, const float* correction, int tokens, int outputs,
@@ -352,22 +436,32 @@ extern "C" int omnia_moe_route(const void* h, const float* router, const float* 
                                cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (top < 1 || top > outputs || experts < 0 || experts > outputs || outputs > 4096) return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)outputs * 2 * sizeof(float);
-  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(moe_route_kernel<T>, tokens, ROUTE_THREADS, smem, stream, (const T*)h, router,
-                                          correction, outputs, experts, hidden, top, choice, weight, counts)));
-  return OMNIA_LAUNCH_RESULT();
+  const int padded = (outputs + 3) / 4 * 4;
+  auto bytes = [&](int tok) { return ((size_t)tok * hidden + (size_t)2 * tok * padded) * sizeof(float); };
+  // Eight tokens a block where there are enough tokens to fill the GPU so and their rows fit.
+  const bool many = tokens >= 8 * omnia_sm_count() && bytes(8) <= 160 * 1024;
+  if (bytes(1) > 200 * 1024) return (int)cudaErrorInvalidValue;
+  OMNIA_DISPATCH_DTYPE(dtype, {
+    if (many)
+      return launch_route<T, 8>((const T*)h, router, correction, tokens, outputs, experts, hidden, top, choice, weight,
+                                counts, bytes(8), stream);
+    return launch_route<T, 1>((const T*)h, router, correction, tokens, outputs, experts, hidden, top, choice, weight,
+                              counts, bytes(1), stream);
+  });
+  return (int)cudaErrorInvalidValue;
 }
 
 extern "C" int omnia_moe_tile_rows() { return TILE_ROWS; }
 
-// After `route`: the sorted order (offsets, place, source) and the tile list of the grouped products.
+// After `route`: the sorted order (offsets, place, source) and the list of row tiles (of at most `tile_rows`
+// rows: omnia_moe_tile_rows() for this file's products, 128 for the tcgen05 kernel's grouped form).
 extern "C" int omnia_moe_plan(const int* choice, int* counts, int* cursors, int* offsets, int* tiles, int* tile_count,
                               int* place, int* source, int tokens, int top, int experts, int max_tiles,
-                              cudaStream_t stream) {
+                              int tile_rows, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  if (experts < 1 || experts > 4096) return (int)cudaErrorInvalidValue;
+  if (experts < 1 || experts > 4096 || tile_rows < 1) return (int)cudaErrorInvalidValue;
   launch_pdl(moe_plan_kernel, 1, 256, (size_t)(experts + 1) * 2 * sizeof(int), stream, counts, cursors, offsets, tiles,
-             tile_count, experts, max_tiles);
+             tile_count, experts, max_tiles, tile_rows);
   const int pairs = tokens * top;
   launch_pdl(moe_scatter_kernel, (pairs + 255) / 256, 256, 0, stream, choice, (const int*)offsets, cursors, place, source,
              pairs, top, experts);
@@ -382,12 +476,22 @@ extern "C" int omnia_moe_product(const void* a, const int* source, const void* w
   const dim3 grid(max_tiles, (n + 63) / 64);
   if (tensor_cores) {
     if (dtype != OMNIA_BF16 || k % 8 != 0 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorInvalidValue;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(moe_product_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)tc_smem_bytes(true));
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(moe_product_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)tc_smem_bytes(false));
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
     if (dual)
-      launch_pdl(moe_product_tc_kernel<true>, grid, 128, 0, stream, (const bf16*)a, source, (const bf16*)w, (bf16*)out,
-                 tiles, tile_count, n, k);
+      launch_pdl(moe_product_tc_kernel<true>, grid, 128, tc_smem_bytes(true), stream, (const bf16*)a, source,
+                 (const bf16*)w, (bf16*)out, tiles, tile_count, n, k);
     else
-      launch_pdl(moe_product_tc_kernel<false>, grid, 128, 0, stream, (const bf16*)a, source, (const bf16*)w, (bf16*)out,
-                 tiles, tile_count, n, k);
+      launch_pdl(moe_product_tc_kernel<false>, grid, 128, tc_smem_bytes(false), stream, (const bf16*)a, source,
+                 (const bf16*)w, (bf16*)out, tiles, tile_count, n, k);
     return OMNIA_LAUNCH_RESULT();
   }
   OMNIA_DISPATCH_DTYPE(dtype, {
@@ -398,6 +502,34 @@ extern "C" int omnia_moe_product(const void* a, const int* source, const void* w
       launch_pdl(moe_product_kernel<T, false>, grid, 256, 0, stream, (const T*)a, source, (const T*)w, (T*)out, tiles,
                  tile_count, n, k);
   });
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// rows[r] = h[source[r]] for the first offsets[experts] rows: the sorted order made contiguous, for a
+// product that reads its operand through a tensor map.
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ source, const int* __restrict__ total,
+                                  T* __restrict__ rows, int hidden) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  if (r >= *total) return;
+  const T* src = h + (size_t)source[r] * hidden;
+  T* dst = rows + (size_t)r * hidden;
+  if ((hidden * sizeof(T)) % 16 == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)rows & 15) == 0) {
+    const int chunks = hidden * (int)sizeof(T) / 16;
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+extern "C" int omnia_moe_gather(const void* h, const int* source, const int* total, void* rows, int pairs, int hidden,
+                                int dtype, cudaStream_t stream) {
+  if (pairs == 0) return 0;
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(moe_gather_kernel<T>, pairs, 128, 0, stream, (const T*)h, source, total,
+                                          (T*)rows, hidden)));
   return OMNIA_LAUNCH_RESULT();
 }
 

@@ -1334,26 +1334,37 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | 
 
 
 MOE_TILE_ROWS = 64
-"""Rows of a tile of the grouped products (csrc/moe.cu)."""
+"""Rows of a tile of the grouped products of csrc/moe.cu (the tcgen05 kernel's grouped form takes 128)."""
+
+MOE_TCGEN05_PAIRS = 1024
+"""From this many (row, choice) pairs on, and at least 64 of them an expert on average, the bfloat16
+grouped products run on the tcgen05 kernel (tiles of 128 rows of one expert each; fewer rows an expert
+would leave most of every tile empty); below, on the mma.sync kernel with tiles of 64 rows."""
 
 
 def moe_experts(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, gate_up: torch.Tensor,
                 down: torch.Tensor, top: int, step: StepContext | None = None,
-                tensor_cores: bool | None = None) -> torch.Tensor:
+                tensor_cores: bool | None = None, tcgen05: bool | None = None) -> torch.Tensor:
     """A routed mixture of gated feed-forward experts over the rows of `h` [rows, hidden]:
     y = sum over a row's `top` choices of score * expert(h), expert e being
     down[e] (silu(gate_e h) * (up_e h)) with gate_up [experts, 2 inner, hidden] (gate rows, then up
     rows) and down [experts, hidden, inner]; router outputs beyond the experts with tensors are
     identity experts (their output is h). Nothing is asked of the host: rows are sorted by expert on
     the device, and the grouped products walk a tile list made there. bfloat16 runs on the tensor
-    cores (`tensor_cores` False keeps it off), float32 on the ordinary ones."""
+    cores: the tcgen05 kernel's grouped form for many rows (`tcgen05` names the choice), mma.sync for
+    few (`tensor_cores` False keeps both off); float32 on the ordinary cores."""
     rows, hidden = h.shape
     experts, inner = gate_up.shape[0], gate_up.shape[1] // 2
     pairs = rows * top
-    max_tiles = min(pairs, -(-pairs // MOE_TILE_ROWS) + experts)
     device = h.device
     if step is None:
         step = _NoStep()
+    if tensor_cores is None:
+        tensor_cores = h.dtype == torch.bfloat16 and hidden % 8 == 0 and inner % 8 == 0
+    if tcgen05 is None:
+        tcgen05 = tensor_cores and pairs >= MOE_TCGEN05_PAIRS and pairs >= 64 * experts
+    tile_rows = 128 if tcgen05 else MOE_TILE_ROWS
+    max_tiles = min(pairs, -(-pairs // tile_rows) + experts)
     counts, cursors = _step_buffers(step, device, {"moe_counts": (experts, torch.int32, True),
                                                    "moe_cursors": (experts, torch.int32, True)})
     choice, weight = moe_route(h, router, correction, experts, top, counts)
@@ -1364,20 +1375,32 @@ def moe_experts(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor 
     tile_count = ints[-1:]
     fn = _function("moe", "omnia_moe_plan",
                    [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                    c_int, c_void_p])
+                    c_int, c_int, c_void_p])
     _check(fn(_ptr(choice), _ptr(counts), _ptr(cursors), _ptr(offsets), _ptr(tiles), _ptr(tile_count), _ptr(place),
-              _ptr(source), rows, top, experts, max_tiles, _stream()), "moe_plan")
-    if tensor_cores is None:
-        tensor_cores = h.dtype == torch.bfloat16 and hidden % 8 == 0 and inner % 8 == 0
-    product = _function("moe", "omnia_moe_product",
-                        [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                         c_int, c_void_p])
+              _ptr(source), rows, top, experts, max_tiles, tile_rows, _stream()), "moe_plan")
     act = torch.empty(pairs, inner, dtype=h.dtype, device=device)
-    _check(product(_ptr(h), _ptr(source), _ptr(gate_up), _ptr(act), _ptr(tiles), _ptr(tile_count), max_tiles, inner,
-                   hidden, 1, _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
     out = torch.empty(pairs, hidden, dtype=h.dtype, device=device)
-    _check(product(_ptr(act), None, _ptr(down), _ptr(out), _ptr(tiles), _ptr(tile_count), max_tiles, hidden, inner, 0,
-                   _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
+    if tcgen05:
+        sorted_rows = torch.empty(pairs, hidden, dtype=h.dtype, device=device)
+        fn = _function("moe", "omnia_moe_gather", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check(fn(_ptr(h), _ptr(source), _ptr(offsets[experts:]), _ptr(sorted_rows), pairs, hidden, _code(h.dtype),
+                  _stream()), "moe_gather")
+        grouped = _function("gemm_tcgen05", "omnia_gemm_tcgen05_grouped",
+                            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                             c_void_p, c_void_p])
+        err = _ptr(error_word(device))
+        _check(grouped(_ptr(sorted_rows), _ptr(gate_up), _ptr(act), pairs, 2 * inner, hidden, experts, 1, _ptr(tiles),
+                       _ptr(tile_count), max_tiles, err, _stream()), "gemm_tcgen05_grouped")
+        _check(grouped(_ptr(act), _ptr(down), _ptr(out), pairs, hidden, inner, experts, 0, _ptr(tiles),
+                       _ptr(tile_count), max_tiles, err, _stream()), "gemm_tcgen05_grouped")
+    else:
+        product = _function("moe", "omnia_moe_product",
+                            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                             c_int, c_void_p])
+        _check(product(_ptr(h), _ptr(source), _ptr(gate_up), _ptr(act), _ptr(tiles), _ptr(tile_count), max_tiles, inner,
+                       hidden, 1, _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
+        _check(product(_ptr(act), None, _ptr(down), _ptr(out), _ptr(tiles), _ptr(tile_count), max_tiles, hidden, inner, 0,
+                       _code(h.dtype), int(tensor_cores), _stream()), "moe_product")
     y = torch.empty_like(h)
     fn = _function("moe", "omnia_moe_combine",
                    [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])

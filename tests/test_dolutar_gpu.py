@@ -253,7 +253,8 @@ def test_clamped_gated_unit(dtype):
 
 @pytest.mark.parametrize("dtype,tensor_cores", [("float32", False), ("bfloat16", True), ("bfloat16", False)])
 @pytest.mark.parametrize("rows,hidden,inner,experts,identity,top", [(50, 96, 24, 5, 2, 2), (1, 64, 40, 3, 0, 1),
-                                                                  (200, 128, 72, 9, 3, 4), (3, 64, 8, 2, 5, 3)])
+                                                                  (200, 128, 72, 9, 3, 4), (3, 64, 8, 2, 5, 3),
+                                                                  (700, 192, 136, 3, 1, 2)])
 def test_routed_experts(dtype, tensor_cores, rows, hidden, inner, experts, identity, top):
     """Router, sorted order, grouped products and the weighted sum, on the ordinary cores and on the
     tensor cores, against the plain function; the buffers that must be zero between calls are."""
@@ -274,6 +275,11 @@ def test_routed_experts(dtype, tensor_cores, rows, hidden, inner, experts, ident
         got = ops.moe_experts(h.to(CUDA), W["m.router"].to(CUDA), W["m.correction"].to(CUDA), gate_up, down, top,
                               tensor_cores=tensor_cores)
         assert rel(got, want) < (2e-5 if dtype == "float32" else 2.5e-2)
+    if tensor_cores:  # the same on the tcgen05 kernel's grouped form, whatever the number of rows
+        got = ops.moe_experts(h.to(CUDA), W["m.router"].to(CUDA), W["m.correction"].to(CUDA), gate_up, down, top,
+                              tcgen05=True)
+        assert rel(got, want) < 2.5e-2
+        ops.raise_on_error(CUDA)
     counts = torch.zeros(experts, dtype=torch.int32, device=CUDA)
     choice, weight = ops.moe_route(h.to(CUDA), W["m.router"].to(CUDA), W["m.correction"].to(CUDA), experts, top, counts)
     chosen, weights = plain.route(h.double(), W, "m.", top)
