@@ -21,23 +21,22 @@
 
 namespace {
 
-constexpr int ROUTE_THREADS = 256;
 constexpr int TILE_ROWS = 64;  // rows of a tile of the grouped products
 
 // ---------------------------------------------------------------------------------
 // A block routes TOK consecutive tokens (8 where there are many: every router row is then fetched
-// once for eight tokens instead of once a token; 1 in a small step, which wants blocks, not reuse).
+// once for eight tokens instead of once a token; 1 in a small step, which wants warps, not reuse).
 // The tokens' rows wait in shared memory as float32; a warp owns every eighth router output and takes
-// the dot products of four of them with all TOK rows in one pass over the columns.
+// the dot products of CHUNK of them with all TOK rows in one pass over the columns.
 // Then warp t finishes token t: softmax over all outputs, choice scores, the `top` largest.
-template <typename T, int TOK>
-__global__ void __launch_bounds__(ROUTE_THREADS)
+template <typename T, int TOK, int THREADS, int CHUNK>
+__global__ void __launch_bounds__(THREADS)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, const float* __restrict__ correction,
                  int tokens, int outputs, int experts, int hidden, int top, int* __restrict__ choice,
                  float* __restrict__ weight, int* __restrict__ counts) {
   pdl_wait();
   pdl_launch_dependents();
-  constexpr int WARPS = ROUTE_THREADS / 32;
+  constexpr int WARPS = THREADS / 32;
   static_assert(TOK <= WARPS, "a warp finishes a token");
   extern __shared__ __align__(16) float route_s[];
   const int padded = (outputs + 3) / 4 * 4;
@@ -46,13 +45,13 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = blockIdx.x * TOK, live = min(TOK, tokens - t0);
   for (int tok = 0; tok < TOK; ++tok)
-    for (int i = threadIdx.x; i < hidden; i += ROUTE_THREADS)
+    for (int i = threadIdx.x; i < hidden; i += THREADS)
       hrow[(size_t)tok * hidden + i] = tok < live ? to_f32(h[(size_t)(t0 + tok) * hidden + i]) : 0.f;
   __syncthreads();
-  // Four router outputs a warp at a time (outputs warp, warp + 8, ...): a lane reads a float4 of each
-  // token's row once and uses it against all four, and the four loads of the router's rows, times
-  // the unrolling, are in flight together.
-  constexpr int CHUNK = 4;
+  // CHUNK router outputs a warp at a time (outputs warp, warp + WARPS, ...): a lane reads a float4 of
+  // each token's row once and uses it against all of them, and the CHUNK loads of the router's rows,
+  // times the unrolling, are in flight together. (A single token: 32 warps, an output each, eight
+  // steps of the columns in flight: the router's rows come from memory, and the block is their latency.)
   const bool wide = (hidden & 3) == 0 && ((uintptr_t)router & 15) == 0;
   for (int e0 = warp; e0 < outputs; e0 += WARPS * CHUNK) {
     float acc[CHUNK][TOK];
@@ -64,7 +63,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
       const int quads = hidden / 4;
       const float4* w4 = reinterpret_cast<const float4*>(router);
       const float4* h4 = reinterpret_cast<const float4*>(hrow);
-#pragma unroll 2
+#pragma unroll(CHUNK == 1 ? 8 : 2)
       for (int q = lane; q < quads; q += 32) {
         float4 b[CHUNK];
 #pragma unroll
@@ -417,14 +416,15 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const T* __restri
   }
 }
 
-template <typename T, int TOK>
+template <typename T, int TOK, int THREADS, int CHUNK>
 int launch_route(const T* h, const float* router, const float* correction, int tokens, int outputs, int experts,
                  int hidden, int top, int* choice, float* weight, int* counts, size_t smem, cudaStream_t stream) {
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(moe_route_kernel<T, TOK, THREADS, CHUNK>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  launch_pdl(moe_route_kernel<T, TOK>, (tokens + TOK - 1) / TOK, ROUTE_THREADS, smem, stream, h, router, correction, tokens,
+  launch_pdl(moe_route_kernel<T, TOK, THREADS, CHUNK>, (tokens + TOK - 1) / TOK, THREADS, smem, stream, h, router, correction, tokens,
              outputs, experts, hidden, top, choice, weight, counts);
   return OMNIA_LAUNCH_RESULT();
 }
@@ -443,9 +443,9 @@ extern "C" int omnia_moe_route(const void* h, const float* router, const float* 
   if (bytes(1) > 200 * 1024) return (int)cudaErrorInvalidValue;
   OMNIA_DISPATCH_DTYPE(dtype, {
     if (many)
-      return launch_route<T, 8>((const T*)h, router, correction, tokens, outputs, experts, hidden, top, choice, weight,
+      return launch_route<T, 8, 256, 4>((const T*)h, router, correction, tokens, outputs, experts, hidden, top, choice, weight,
                                 counts, bytes(8), stream);
-    return launch_route<T, 1>((const T*)h, router, correction, tokens, outputs, experts, hidden, top, choice, weight,
+    return launch_route<T, 1, 1024, 1>((const T*)h, router, correction, tokens, outputs, experts, hidden, top, choice, weight,
                               counts, bytes(1), stream);
   });
   return (int)cudaErrorInvalidValue;
