@@ -87,7 +87,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out,
                                  float* __restrict__ partial, int* __restrict__ tickets,
                                  int max_pages, int num_pages, int nq, int nkv, int page_size, int window,
-                                 float scale, int* err) {
+                                 float scale, int keep_first, const float* __restrict__ sink, int* err) {
   if (work[WORK_INTS * blockIdx.x] < 0) return;  // a place of the list that this step does not use
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // The swizzled tiles need a base on 1024 bytes; the dynamic area starts on one (nothing static
@@ -117,9 +117,23 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
   const int last = pos0 + tokens - 1;                                   // last key any row sees
   const int first = window > 0 ? max(0, pos0 - window + 1) : 0;         // first key any row sees
   const int last_tile = last / BN;
-  const int tile0 = first / BN + (item[4] < 0 ? 0 : item[3]);
-  const int n_tiles = item[4] < 0 ? last_tile - tile0 + 1 : item[4];
+  // Kept first positions (a window that leaves the first `keep_first` positions visible): when some
+  // row's window begins after position 0, the block first walks the tiles of the kept keys (every row
+  // sees keys below keep_first there, up to its own position), then the tiles of the window, in which
+  // a row sees [max(its window's first key, keep_first), its position]: a tile may come twice, no key
+  // counts twice, and every row's visible keys of a tile stay one run. Such a block is listed whole.
+  const bool keeps = keep_first > 0 && window > 0 && last - window + 1 > 0;
+  const int kept_tiles = keeps ? (min(keep_first, last + 1) + BN - 1) / BN : 0;
+  const int first_w = keeps ? max(first, keep_first) : first;  // the window's tiles hold keys from here on
+  const int tile0 = first_w / BN + (item[4] < 0 ? 0 : item[3]);
+  const int n_tiles = item[4] < 0 ? kept_tiles + max(last_tile - tile0 + 1, 0) : item[4];
   const bool whole = parts <= 1;  // this block does all of its rows' keys and stores the result itself
+  if ((keeps || sink != nullptr) && !whole) {
+    if (threadIdx.x == 0) atomicOr(err, OMNIA_ERR_WORK);  // parts are merged without a sink and walk one run of tiles
+    return;
+  }
+  // Tile j of the block's list as a tile of absolute key positions.
+  auto tile_of = [&](int j) { return j < kept_tiles ? j : tile0 + j - kept_tiles; };
 
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, k_full0 = bar0 + 8, v_full0 = k_full0 + 8 * K_STAGES, v_done0 = v_full0 + 8 * V_STAGES,
@@ -167,8 +181,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // The page of this lane's group in tile t (-2: the group lies outside what the block reads).
     // Page numbers are fetched a whole tile before they are used, so the table's latency is hidden.
     auto lookup = [&](int t) {
-      const int pos = (tile0 + t) * BN + g * 16;
-      return (active && t < n_tiles && pos <= last && pos + 15 >= first) ? table[pos / page_size] : -2;
+      const int pos = tile_of(t) * BN + g * 16;
+      const bool wanted = t < kept_tiles ? pos < keep_first && pos <= last : pos <= last && pos + 15 >= first_w;
+      return (active && t < n_tiles && wanted) ? table[pos / page_size] : -2;
     };
     bool ok = true;
     int issued = 0;
@@ -181,11 +196,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) return;
       if (lane == 0) STAMP(0, j, which * 2);
-      const int pos = (tile0 + j) * BN + g * 16;
+      const int pos = tile_of(j) * BN + g * 16;
       bool load = page != -2;
       if (load && (page < 0 || page >= num_pages)) {
         // A page behind the window may have been given back; one the block really reads may not.
-        if (pos >= first) atomicOr(err, OMNIA_ERR_PAGE);
+        if (pos >= first || j < kept_tiles) atomicOr(err, OMNIA_ERR_PAGE);
         load = false;
       }
       const uint32_t loaded = __ballot_sync(0xffffffffu, load);
@@ -299,7 +314,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     float m = -INFINITY, l = 0.f;
     bool ok = true, gate_issued = false;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int key0 = (tile0 + j) * BN;
+      const int key0 = tile_of(j) * BN;
       ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -316,7 +331,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       if (row == 0) STAMP(2, j, 0);
       const uint32_t s_addr = tmem_base + lane_field + S_COL + (j & 1) * BN;
       // Which keys of the tile this row sees; a tile that the whole warp sees whole needs no masks.
-      const int lo = max(row_lo - key0, 0), hi = min(row_hi - key0, BN - 1);  // visible columns [lo, hi]
+      const int see_lo = j < kept_tiles ? 0 : keeps ? max(row_lo, keep_first) : row_lo;
+      const int see_hi = j < kept_tiles ? min(row_hi, keep_first - 1) : row_hi;
+      const int lo = max(see_lo - key0, 0), hi = min(see_hi - key0, BN - 1);  // visible columns [lo, hi]
       const bool unmasked = __all_sync(0xffffffffu, lo == 0 && hi == BN - 1);
       // The row's 64 scores, read once; then their maximum.
       static_assert(BN == 64, "the softmax below handles one 64-column pass per tile");
@@ -398,7 +415,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       tmem_store32(s_addr, packed);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       l += sum;
-      if (tile0 + j == last_tile && ((last + 1) & 15)) {
+      if (tile_of(j) == last_tile && ((last + 1) & 15)) {
         // The last group of 16 keys reaches past the block's last key. Those rows of V get a
         // zero weight, but what they hold need not be a number: past the request's last token
         // the page still holds whatever its previous owner left (0 x NaN is NaN). Clear them in
@@ -484,6 +501,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
       // 64 dims of the row's accumulator in one go (two loads side by side; eight dims a turn with the
       // next turn's columns on their way took longer: every turn waited for a load), then eight dims
       // at a time: normalise, gate, 16 bytes stored.
+      // A sink: one more term exp(sink) of the row's denominator, with no value (l is kept against the offset m).
+      if (sink != nullptr && m != -INFINITY) l += exp2f(sink[head] * LOG2E - m * sl2);
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = out + (token * nq + head) * D;
       const uint32_t o_addr = tmem_base + lane_field + O_COL;
@@ -622,9 +641,11 @@ extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const 
                                                int blocks, const void* gate, int gate_stride, void* out,
                                                float* partial, int* tickets,
                                                int max_pages, int num_pages, int nq, int nkv, int page_size,
-                                               int window, float scale, int* err, cudaStream_t stream) {
+                                               int window, float scale, int keep_first, const float* sink, int* err,
+                                               cudaStream_t stream) {
   if (blocks == 0) return 0;
-  if (nq != nkv * GROUP || page_size % 16 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)pages & 15))
+  if (nq != nkv * GROUP || page_size % 16 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)pages & 15) || keep_first < 0 ||
+      (keep_first > 0 && window <= 0))
     return (int)cudaErrorInvalidValue;
   CUtensorMap map_q, map_kv, map_gate;
   int gate_tma = 0;
@@ -641,6 +662,6 @@ extern "C" int omnia_attention_prefill_tcgen05(const void* q, int tokens, const 
   }
   launch_pdl(attention_prefill_tcgen05_kernel, blocks, THREADS, smem, stream,
              map_q, map_kv, map_gate, gate_tma, block_table, cu_seqlens, seq_lens, work, (const bf16*)gate, gate_stride, (bf16*)out,
-             partial, tickets, max_pages, num_pages, nq, nkv, page_size, window, scale, err);
+             partial, tickets, max_pages, num_pages, nq, nkv, page_size, window, scale, keep_first, sink, err);
   return OMNIA_LAUNCH_RESULT();
 }

@@ -593,9 +593,10 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
     `sink` (float32 [nq]) adds exp(sink[head]) to every row's denominator. A cache whose spec names
     `keep_first` keeps that many first positions visible behind the window; `window` and `keep_first`,
     when given, are the mixer's own and replace the cache's (a mixer that reads another's cache may
-    see less of it than is kept). Sink and kept positions are taken by the generic
-    and the mma.sync kernels (not by the tcgen05 ones); values of another width than the keys run on
-    the generic kernel.
+    see less of it than is kept). Sink and kept positions are taken by the generic kernel, by the
+    mma.sync kernels and by the tcgen05 prefill kernel that runs two blocks to an SM (every block is
+    then listed whole), not by the one that gives a block its SM; values of another width than the
+    keys run on the generic kernel.
 
     With `projection` (only where `decode_fusable` holds) q is not given: the kernel makes the
     queries and the new keys and values from the projected rows, and writes the latter to the cache.
@@ -660,11 +661,14 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
                   kv.window or 0, scale, warps, *fused, 1, keep, _ptr(sink), err, _stream()), "attention_decode")
         if step.decode_only or all(n == 1 for n in step.q_lens):
             return out
-    if sink is None and not keep and tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
+    if tcgen05_attention_supported(q.dtype, nq, nkv, d, kv.page_size):
         per_block = 128 // (nq // nkv)
         sms = sm_count(q.device)
+        plain = sink is None and not keep  # a sink or kept first positions: the two-to-an-SM kernel, every block whole
         if wide is None:
-            wide = wide_prefill_pays(step.q_lens, step.seq_lens_host, per_block, nkv, kv.window or 0, sms)
+            wide = plain and wide_prefill_pays(step.q_lens, step.seq_lens_host, per_block, nkv, kv.window or 0, sms)
+        elif wide and not plain:
+            raise KernelError("the kernel that gives a block its SM takes neither a sink nor kept first positions")
         if wide:
             # Every block whole (no places to share tiles over), an SM to a block.
             work = _prefill_work_flat(step, per_block, 64, nkv, kv.window or 0, q.device, 0)
@@ -675,7 +679,7 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
                       _ptr(work), work.shape[0], gate_ptr, gate_stride, _ptr(out), max_pages, num_pages, nq, nkv,
                       kv.page_size, kv.window or 0, scale, err, _stream()), "attention_prefill_tcgen05_wide")
             return out
-        work = _prefill_work_flat(step, per_block, 64, nkv, kv.window or 0, q.device, prefill_places(sms))
+        work = _prefill_work_flat(step, per_block, 64, nkv, kv.window or 0, q.device, prefill_places(sms) if plain else 0)
         # Room for the parts of blocks that are cut (at most one more item per block the device runs at
         # a time) and a ticket per block; the sizes do not depend on the contexts' lengths.
         part_floats = _function("attention_tcgen05", "omnia_attention_tcgen05_part_floats", [], defines)()
@@ -685,11 +689,12 @@ def paged_attention(q: torch.Tensor | None, kv: KVView, step: StepContext, scale
             "prefill_tickets": (base, torch.int32, True)})
         fn = _function("attention_tcgen05", "omnia_attention_prefill_tcgen05",
                        [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
-                       defines)
+                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                        c_void_p, c_void_p], defines)
         _check(fn(_ptr(q), tokens, _ptr(kv.pages), _ptr(kv.block_table), _ptr(step.cu_seqlens), _ptr(step.seq_lens),
                   _ptr(work), work.shape[0], gate_ptr, gate_stride, _ptr(out), _ptr(partial), _ptr(tickets), max_pages,
-                  num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, err, _stream()), "attention_prefill_tcgen05")
+                  num_pages, nq, nkv, kv.page_size, kv.window or 0, scale, keep, _ptr(sink), err, _stream()),
+               "attention_prefill_tcgen05")
         return out
     tokens_per_block = 64 // (nq // nkv)
     work = _prefill_work(step, tokens_per_block, q.device)

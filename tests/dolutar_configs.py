@@ -57,6 +57,12 @@ CONFIGS = {
           "embedding": {"scale": 5.0, "bigram": {"buckets": 53, "mul_prev": 7, "mul_cur": 9}},
           "layers": [_dense(_attention(4, 2, 16, 16, 8, 150, 70, 0.25), 64, 1.5),
                      _moe(_attention(4, 1, 24, 24, 12, 64, 33, 0.2), 32, 6, 2, 2)]},
+    # heads of 64 and pages of 16: in bfloat16 the prompts' attention runs on the tcgen05 kernel
+    "S": {"architecture": "Dolutar", "vocab": 180, "width": 128, "logit_scale": 0.7, "norm": {"eps": 1e-5},
+          "embedding": {"scale": 4.0, "bigram": {"buckets": 89, "mul_prev": 5, "mul_cur": 3}},
+          "layers": [_dense(_attention(4, 2, 64, 64, 32, 70, 9, 0.125), 96, 1.2),
+                     _moe(_attention(4, 2, 64, 64, 32, 33, 70, 0.125, kv_from=0), 48, 4, 1, 2),
+                     _dense(_attention(3, 1, 64, 64, 64, 130, 0, 0.125), 64, 3.0)]},
 }
 
 

@@ -159,7 +159,9 @@ def _filled(spec, pages, K, V, page, order):
 
 
 ATTENTION_CASES = [("float32", 4, 2, 16, 24, 4), ("bfloat16", 6, 1, 16, 16, 16), ("bfloat16", 4, 2, 64, 64, 16),
-                   ("bfloat16", 2, 2, 24, 8, 8), ("float32", 2, 1, 32, 32, 16)]
+                   ("bfloat16", 2, 2, 24, 8, 8), ("float32", 2, 1, 32, 32, 16), ("bfloat16", 8, 2, 128, 128, 16),
+                   ("bfloat16", 4, 2, 64, 64, 8)]
+# (heads of 64 and 128 over pages of 16: the prompts' portions run on the tcgen05 kernel; over pages of 8 on mma.sync)
 
 
 @pytest.mark.parametrize("dtype,H,G,dk,dv,page", ATTENTION_CASES)
@@ -370,6 +372,32 @@ def test_portions_decoding_and_mixed_batches(tmp_path, name, page, dtype):
         positions, logits = stacked(got[r])
         assert positions == list(range(len(ids[r])))
         assert_rows(logits, plain.forward(ids[r], weights, raw), dtype, r)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_heads_of_64_over_pages_of_16(tmp_path, dtype):
+    """Sizes at which bfloat16 prompts take the tcgen05 attention kernel: whole prompts from 1 to 400
+    tokens (kept positions beyond, at and inside the window's first tile), portions over a context,
+    single tokens beside portions, a reader whose kept positions outnumber its owner's."""
+    raw, weights, engine = engine_for("S", dtype, page=16, tokens=1536)
+    for n in (1, 9, 70, 71, 140, 400):
+        ids = dc.prompt(n, raw["vocab"], n)
+        request = engine.cache.open("r")
+        got = engine.runner.run([StepEntry(request, ids, list(range(n)))])
+        engine.cache.close("r")
+        assert_rows(got, plain.forward(ids, weights, raw), dtype, n)
+    ids = {"a": dc.prompt(330, raw["vocab"], 1), "b": dc.prompt(90, raw["vocab"], 2), "c": dc.prompt(40, raw["vocab"], 3)}
+    trace = Trace()
+    trace.step({"a": ids["a"][:130]})
+    trace.step({"a": ids["a"][130:263], "b": ids["b"][:64]})
+    trace.step({"a": ids["a"][263:264], "b": ids["b"][64:90], "c": ids["c"][:2]}, end=["b"])
+    trace.step({"a": ids["a"][264:330], "c": ids["c"][2:40]}, end=["a", "c"])
+    got = trace.run_engine(engine, tmp_path / "out", before_step=lambda e, record: poison_free_pages(e))
+    for r in ids:
+        positions, logits = stacked(got[r])
+        assert positions == list(range(len(ids[r])))
+        assert_rows(logits, plain.forward(ids[r], weights, raw), dtype, r)
+    ops.raise_on_error(CUDA)
 
 
 @pytest.mark.parametrize("name", ["P", "Q"])
