@@ -279,10 +279,10 @@ moe_product_kernel(const T* __restrict__ a, const int* __restrict__ source, cons
 // double buffer; k % 8 == 0 and operands whose rows start on 16 bytes.
 typedef __nv_bfloat16 bf16;
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+// A 16-byte asynchronous copy to a shared-memory address; not valid: the 16 bytes are zero-filled.
+__device__ __forceinline__ void cp_async16_to(uint32_t smem, const void* gmem, bool valid) {
   const int bytes = valid ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem), "l"(gmem), "r"(bytes));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
@@ -325,18 +325,40 @@ moe_product_tc_kernel(const bf16* __restrict__ a, const int* __restrict__ source
   if (tid < TILE_ROWS) src_row[tid] = tid < rows ? (source ? source[row0 + tid] : row0 + tid) : -1;
   __syncthreads();
   const bf16* we = w + (size_t)expert * PARTS * n * k;
-  auto load = [&](int k0, int stage) {
-    // 64 rows x 4 chunks of 16 bytes for A, and for each part of B: 128 threads, 2 rounds each.
-    for (int i = tid; i < TILE_ROWS * 4; i += 128) {
-      const int r = i >> 2, c = i & 3;
-      const int src = src_row[r];
-      const bool live = src >= 0 && k0 + c * 8 < k;
-      cp_async16(&As[stage][r][c * 8], live ? a + (size_t)src * k + k0 + c * 8 : a, live);
+  // A stage is 64 rows x 4 chunks of 16 bytes of A and of each part of B: a thread copies two chunks of
+  // each (rows tid / 4 and 32 + tid / 4, chunk tid % 4), and where they come from and go to is worked out
+  // once: a step of the loop is then a copy, an add and a test a chunk. (With one or two rows a tile the
+  // kernel is a stream of weights that the issue of its own instructions bounds: 2.6 TB/s with the
+  // addresses recomputed every step.) Rows of A beyond the tile's own are not copied at all: a row of
+  // the product depends on its own row of A only, and theirs is never stored.
+  constexpr uint32_t A_STAGE = TILE_ROWS * ROW * sizeof(bf16), B_STAGE = PARTS * 64 * ROW * sizeof(bf16);
+  const int chunk = (tid & 3) * 8;
+  const bf16* a_src[2];
+  const bf16* b_src[2][PARTS];
+  uint32_t a_dst[2], b_dst[2][PARTS];
+  bool a_on[2], b_on[2];
 #pragma unroll
-      for (int part = 0; part < PARTS; ++part) {
-        const bool liveb = n0 + r < n && k0 + c * 8 < k;
-        cp_async16(&Bs[stage][part][r][c * 8], liveb ? we + (size_t)(part * n + n0 + r) * k + k0 + c * 8 : w, liveb);
-      }
+  for (int slot = 0; slot < 2; ++slot) {
+    const int r = slot * 32 + (tid >> 2);
+    const int src = src_row[r];
+    a_on[slot] = src >= 0;
+    a_src[slot] = a + (size_t)(src >= 0 ? src : 0) * k + chunk;
+    a_dst[slot] = (uint32_t)__cvta_generic_to_shared(&As[0][r][chunk]);
+    b_on[slot] = n0 + r < n;
+#pragma unroll
+    for (int part = 0; part < PARTS; ++part) {
+      b_src[slot][part] = we + (size_t)(part * n + (b_on[slot] ? n0 + r : 0)) * k + chunk;
+      b_dst[slot][part] = (uint32_t)__cvta_generic_to_shared(&Bs[0][part][r][chunk]);
+    }
+  }
+  auto load = [&](int k0, int stage) {
+    const bool in_k = k0 + chunk < k;
+#pragma unroll
+    for (int slot = 0; slot < 2; ++slot) {
+      if (a_on[slot]) cp_async16_to(a_dst[slot] + stage * A_STAGE, a_src[slot] + k0, in_k);
+#pragma unroll
+      for (int part = 0; part < PARTS; ++part)
+        cp_async16_to(b_dst[slot][part] + stage * B_STAGE, b_src[slot][part] + k0, b_on[slot] && in_k);
     }
   };
   float acc[PARTS][8][4];
