@@ -63,6 +63,14 @@ CONFIGS = {
           "layers": [_dense(_attention(4, 2, 64, 64, 32, 70, 9, 0.125), 96, 1.2),
                      _moe(_attention(4, 2, 64, 64, 32, 33, 70, 0.125, kv_from=0), 48, 4, 1, 2),
                      _dense(_attention(3, 1, 64, 64, 64, 130, 0, 0.125), 64, 3.0)]},
+    # nothing a multiple of eight: a width of 100, heads of 20 with values of 12, feed-forwards of 30 and
+    # 20, a window of one token, one kept position, a rotation over four dims, three of four experts
+    "O": {"architecture": "Dolutar", "vocab": 101, "width": 100, "logit_scale": 1.5, "norm": {"eps": 1e-5},
+          "embedding": {"scale": 2.0, "bigram": {"buckets": 7, "mul_prev": 1000003, "mul_cur": 999983}},
+          "layers": [_moe(_attention(3, 3, 20, 12, 4, 1, 1, 0.22), 20, 4, 0, 3),
+                     _dense(_attention(3, 3, 20, 12, 4, 6, 1, 0.22, kv_from=0), 30, 0.8),
+                     _bare(_attention(5, 1, 36, 36, 0, 13, 2, 0.17)),
+                     _moe(_attention(3, 3, 20, 12, 4, 2, 0, 0.22, kv_from=0), 12, 1, 3, 2)]},
 }
 
 

@@ -323,7 +323,7 @@ def assert_rows(got, want, dtype, what="", tolerance=None):
         assert float(err.median()) < tolerance / 4, (what, float(err.median()))
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "O"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_whole_prompts(name, dtype):
     raw, weights, engine = engine_for(name, dtype)
@@ -336,7 +336,7 @@ def test_whole_prompts(name, dtype):
     ops.raise_on_error(CUDA)
 
 
-@pytest.mark.parametrize("name,page", [("P", 4), ("Q", 16), ("R", 8)])
+@pytest.mark.parametrize("name,page", [("P", 4), ("Q", 16), ("R", 8), ("O", 16)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_portions_decoding_and_mixed_batches(tmp_path, name, page, dtype):
     """Six requests over four state slots: prompts read whole, in portions of 2 to 9 tokens and
