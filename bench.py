@@ -803,7 +803,7 @@ def dolutar_config(size: dict) -> dict:
              "router": {"experts": size["experts"], "identity": size["identity"], "top": size["top"]}}
         layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
     return {"architecture": "Dolutar", "vocab": DOLUTAR_VOCAB, "width": size["width"], "logit_scale": 1.0,
-            "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+            "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 17}},
             "layers": layers}
 
 
@@ -938,7 +938,7 @@ def run_dolutar(args) -> dict:
             st.token_ids = torch.randint(0, DOLUTAR_VOCAB, (T,), device=dev, dtype=torch.int32)
             emb, pairs = (torch.randn(n, D, device=dev).to(bf) for n in (DOLUTAR_VOCAB, 65522))
             prev = torch.zeros(len(lens) + 1, dtype=torch.int32, device=dev)
-            note(f"embed_pair_{mode}", timed(lambda: ops.embed_pair(st, emb, pairs, prev, 1.0, 31, 7), 20), bytes_=T * D * (2 + 2 + 4))
+            note(f"embed_pair_{mode}", timed(lambda: ops.embed_pair(st, emb, pairs, prev, 1.0, 131, 17), 20), bytes_=T * D * (2 + 2 + 4))
             note(f"like:embed_rmsnorm_{mode}", timed(lambda: ops.embed_rmsnorm(st.token_ids, emb, 1e-6), 20), bytes_=T * D * (2 + 4))
             # bias, head norms, rotation and the cache write, beside the weightless form
             cols = (H + 2 * G) * d
@@ -985,7 +985,7 @@ def run_dolutar(args) -> dict:
 
             note(f"moe_route_{mode}", timed(route, 20), bytes_=T * D * 2 + R * D * 4)
             ms = timed(lambda: ops.moe_experts(h, router, correction, egu, edn, top, st), 10)
-            used = min(E, T * top)  # experts whose weights a step reads at most
+            used = E * (1.0 - (1.0 - top / R) ** T)  # experts that T tokens' choices touch, on average
             note(f"moe_experts_{mode}", ms, bytes_=used * 3 * F * D * 2 + T * D * 4, flops=2 * T * top * 3 * F * D)
             dgu = (torch.randn(2 * top * F, D, device=dev) * D ** -0.5).to(bf)
             ddn = (torch.randn(D, top * F, device=dev) * (top * F) ** -0.5).to(bf)
