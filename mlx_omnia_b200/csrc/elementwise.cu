@@ -611,6 +611,24 @@ extern "C" int omnia_swiglu(const void* gu, void* act, int rows, int inner, int 
 }
 
 // ---------------------------------------------------------------------------------
+// h = x rounded to the element type, for a part that reads the float32 residual itself.
+template <typename T>
+__global__ void round_rows_kernel(const float* __restrict__ x, T* __restrict__ h, long long total) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) h[i] = from_f32<T>(x[i]);
+}
+
+extern "C" int omnia_round_rows(const float* x, void* h, long long total, int dtype, cudaStream_t stream) {
+  if (total == 0) return 0;
+  const long long most = 16LL * omnia_sm_count();
+  const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
+  OMNIA_DISPATCH_DTYPE(dtype, (launch_pdl(round_rows_kernel<T>, blocks, 256, 0, stream, x, (T*)h, total)));
+  return OMNIA_LAUNCH_RESULT();
+}
+
+// ---------------------------------------------------------------------------------
 // The clamped gated unit: g = min(gu[t, i], limit), u = clamp(gu[t, inner + i], -limit, limit);
 // act[t, i] = g * sigmoid(alpha * g) * (u + 1), in float32, rounded once.
 template <typename T>

@@ -146,9 +146,12 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, cons
 // ---------------------------------------------------------------------------------
 // offsets [experts + 1]; tiles [max_tiles, 3] = (expert, first row, rows); tile_count [1];
 // counts and cursors are left zero for the launches that follow.
+// With `choice` given (a small step) the one block goes on to place every (token, choice) itself, which
+// saves the launch of the scatter kernel below.
 __global__ void moe_plan_kernel(int* __restrict__ counts, int* __restrict__ cursors, int* __restrict__ offsets,
                                 int* __restrict__ tiles, int* __restrict__ tile_count, int experts, int max_tiles,
-                                int tile_rows) {
+                                int tile_rows, const int* __restrict__ choice, int* __restrict__ place,
+                                int* __restrict__ source, int pairs, int top) {
   pdl_wait();
   pdl_launch_dependents();
   extern __shared__ int plan_s[];  // [experts + 1] row offsets, [experts + 1] tile offsets
@@ -176,6 +179,20 @@ __global__ void moe_plan_kernel(int* __restrict__ counts, int* __restrict__ curs
     counts[e] = 0;
     cursors[e] = 0;
   }
+  if (choice == nullptr) return;
+  __syncthreads();  // the cursors are zero (this block is the only one that touches them)
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = choice[i];
+    if (e >= experts) {
+      place[i] = -1;
+    } else {
+      const int row = row0[e] + atomicAdd(cursors + e, 1);
+      place[i] = row;
+      source[row] = i / top;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) cursors[e] = 0;
 }
 
 // ---------------------------------------------------------------------------------
@@ -482,9 +499,14 @@ extern "C" int omnia_moe_plan(const int* choice, int* counts, int* cursors, int*
                               int tile_rows, cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (experts < 1 || experts > 4096 || tile_rows < 1) return (int)cudaErrorInvalidValue;
-  launch_pdl(moe_plan_kernel, 1, 256, (size_t)(experts + 1) * 2 * sizeof(int), stream, counts, cursors, offsets, tiles,
-             tile_count, experts, max_tiles, tile_rows);
   const int pairs = tokens * top;
+  if (pairs <= 2048) {  // a small step: the plan's block places the pairs as well
+    launch_pdl(moe_plan_kernel, 1, 256, (size_t)(experts + 1) * 2 * sizeof(int), stream, counts, cursors, offsets, tiles,
+               tile_count, experts, max_tiles, tile_rows, choice, place, source, pairs, top);
+    return OMNIA_LAUNCH_RESULT();
+  }
+  launch_pdl(moe_plan_kernel, 1, 256, (size_t)(experts + 1) * 2 * sizeof(int), stream, counts, cursors, offsets, tiles,
+             tile_count, experts, max_tiles, tile_rows, (const int*)nullptr, (int*)nullptr, (int*)nullptr, 0, 0);
   launch_pdl(moe_scatter_kernel, (pairs + 255) / 256, 256, 0, stream, choice, (const int*)offsets, cursors, place, source,
              pairs, top, experts);
   return OMNIA_LAUNCH_RESULT();

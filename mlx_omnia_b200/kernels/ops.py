@@ -153,7 +153,12 @@ def embed_pair(step: StepContext, table: torch.Tensor, pairs: torch.Tensor, prev
 
 def rounded_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     """The float32 residual `x` as activations of `dtype` (x itself when that is float32)."""
-    return x if dtype == torch.float32 else x.to(dtype)
+    if dtype == torch.float32:
+        return x
+    h = torch.empty(x.shape, dtype=dtype, device=x.device)
+    fn = _function("elementwise", "omnia_round_rows", [c_void_p, c_void_p, c_longlong, c_int, c_void_p])
+    _check(fn(_ptr(x), _ptr(h), x.numel(), _code(dtype), _stream()), "round_rows")
+    return h
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, dtype: torch.dtype) -> torch.Tensor:

@@ -256,7 +256,7 @@ def test_clamped_gated_unit(dtype):
 @pytest.mark.parametrize("dtype,tensor_cores", [("float32", False), ("bfloat16", True), ("bfloat16", False)])
 @pytest.mark.parametrize("rows,hidden,inner,experts,identity,top", [(50, 96, 24, 5, 2, 2), (1, 64, 40, 3, 0, 1),
                                                                   (200, 128, 72, 9, 3, 4), (3, 64, 8, 2, 5, 3),
-                                                                  (700, 192, 136, 3, 1, 2)])
+                                                                  (700, 192, 136, 3, 1, 2), (1100, 64, 24, 6, 1, 2)])
 def test_routed_experts(dtype, tensor_cores, rows, hidden, inner, experts, identity, top):
     """Router, sorted order, grouped products and the weighted sum, on the ordinary cores and on the
     tensor cores, against the plain function; the buffers that must be zero between calls are."""
